@@ -13,7 +13,7 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Mapping, Tuple
+from typing import Any, Callable, Dict, Mapping, Optional, Tuple
 
 from .spec import ModelSpec
 
@@ -29,6 +29,9 @@ class Architecture:
     parse: Callable[[Mapping[str, Any]], Any]
     build_spec: Callable[[Any], ModelSpec]
     kernel_libraries: Tuple[str, ...] = ()      # kernel libraries beyond the common ones that its parts call
+    # Sizes that only the tensors' shapes give: (config dict, {canonical tensor name: shape}) -> config dict with them filled
+    # in.  Called when the model comes from a folder with weights, before ``parse``.
+    sizes_from_shapes: Optional[Callable[[Mapping[str, Any], Mapping[str, Tuple[int, ...]]], Mapping[str, Any]]] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -37,8 +40,8 @@ _ARCHITECTURES: Dict[str, Architecture] = {}
 def register_architecture(name: str, *, model_types: Tuple[str, ...] = (),
                           parse: Callable[[Mapping[str, Any]], Any],
                           build_spec: Callable[[Any], ModelSpec],
-                          kernel_libraries: Tuple[str, ...] = ()) -> Architecture:
-    arch = Architecture(name, tuple(model_types), parse, build_spec, tuple(kernel_libraries))
+                          kernel_libraries: Tuple[str, ...] = (), sizes_from_shapes=None) -> Architecture:
+    arch = Architecture(name, tuple(model_types), parse, build_spec, tuple(kernel_libraries), sizes_from_shapes)
     _ARCHITECTURES[name] = arch
     return arch
 
@@ -92,10 +95,29 @@ def read_config_json(model_dir: str) -> Dict[str, Any]:
     return raw
 
 
+def tensor_shapes(model_dir: str) -> Dict[str, Tuple[int, ...]]:
+    """Canonical tensor name -> shape for every tensor of the folder's ``*.safetensors`` files (headers only); empty when
+    the folder holds none."""
+    from ..weights.loader import canonical_name
+    from ..weights.safetensors_io import SafetensorsError, open_model_files
+    try:
+        files = open_model_files(model_dir)
+    except SafetensorsError:
+        return {}
+    out: Dict[str, Tuple[int, ...]] = {}
+    for f in files:
+        for rawname, entry in f.entries.items():
+            out[canonical_name(rawname)] = tuple(entry.shape)
+        f.close()
+    return out
+
+
 def load_model_config(model_dir: str):
     """Read ``config.json`` → (architecture, typed config, ModelSpec)."""
     raw = read_config_json(model_dir)
     arch = resolve_architecture(raw)
+    if arch.sizes_from_shapes is not None and os.path.isdir(model_dir):
+        raw = arch.sizes_from_shapes(raw, tensor_shapes(model_dir))
     cfg = arch.parse(raw)
     spec = arch.build_spec(cfg)
     spec.validate()

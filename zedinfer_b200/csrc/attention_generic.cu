@@ -14,6 +14,8 @@
 //
 // sinks (optional, float32 per query head): the softmax's denominator also holds exp(sinks[h]), a term with no
 // key and no value; it is added once, after the last tile, relative to the running maximum of the scores.
+//
+// softcap c > 0: a score s (after the scale) becomes c * tanh(s / c) before the softmax.
 #include "zi_common.cuh"
 
 ZI_DEFINE_LAST_ERROR(attention_generic)
@@ -27,7 +29,7 @@ paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, T* 
                        const int* __restrict__ tables, const int* __restrict__ tok_seg,
                        const int* __restrict__ pos, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                        int page_size, int max_blocks, long long page_stride, long long kv_stride, int window,
-                       float scale, const float* __restrict__ sinks) {
+                       float scale, const float* __restrict__ sinks, float softcap) {
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* qs = smem + warp * head_dim;                                     // this warp's query
@@ -65,6 +67,7 @@ paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, T* 
                 for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
             }
             s = dot * scale;
+            if (softcap > 0.0f) s = softcap * tanhf(s / softcap);
         }
         rows[lane] = roff;
         const float m_new = fmaxf(m, warp_max(s));
@@ -100,7 +103,7 @@ paged_attention_kernel(const T* __restrict__ q, const T* __restrict__ cache, T* 
 ZI_EXPORT int zi_paged_attention(const void* q, const void* cache, void* out, int dtype, const int* tables,
                                  const int* tok_seg, const int* pos, int n_tokens, int n_heads, int n_kv_heads,
                                  int head_dim, int page_size, int max_blocks, long long page_stride,
-                                 long long kv_stride, int window, float scale, const float* sinks,
+                                 long long kv_stride, int window, float scale, const float* sinks, float softcap,
                                  cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (head_dim <= 0 || head_dim % 8 != 0 || head_dim > 1024)
@@ -116,15 +119,15 @@ ZI_EXPORT int zi_paged_attention(const void* q, const void* cache, void* out, in
         if (head_dim <= 256)
             paged_attention_kernel<T, 8><<<(unsigned)blocks, WARPS * 32, smem, stream>>>(
                 (const T*)q, (const T*)cache, (T*)out, tables, tok_seg, pos, n_tokens, n_heads, n_kv_heads, head_dim,
-                page_size, max_blocks, page_stride, kv_stride, window, scale, sinks);
+                page_size, max_blocks, page_stride, kv_stride, window, scale, sinks, softcap);
         else if (head_dim <= 512)
             paged_attention_kernel<T, 16><<<(unsigned)blocks, WARPS * 32, smem, stream>>>(
                 (const T*)q, (const T*)cache, (T*)out, tables, tok_seg, pos, n_tokens, n_heads, n_kv_heads, head_dim,
-                page_size, max_blocks, page_stride, kv_stride, window, scale, sinks);
+                page_size, max_blocks, page_stride, kv_stride, window, scale, sinks, softcap);
         else
             paged_attention_kernel<T, 32><<<(unsigned)blocks, WARPS * 32, smem, stream>>>(
                 (const T*)q, (const T*)cache, (T*)out, tables, tok_seg, pos, n_tokens, n_heads, n_kv_heads, head_dim,
-                page_size, max_blocks, page_stride, kv_stride, window, scale, sinks);
+                page_size, max_blocks, page_stride, kv_stride, window, scale, sinks, softcap);
     });
     return zi_check_launch("paged_attention");
 }

@@ -45,6 +45,7 @@ SOURCES: Dict[str, str] = {
     "rowwise": "rowwise.cu",
     "moe": "moe.cu",
     "ssm": "ssm.cu",
+    "linrec": "linrec.cu",
 }
 EXTRA_FLAGS: Dict[str, List[str]] = {}
 EXTRA_LIBS: Dict[str, List[str]] = {}

@@ -7,11 +7,11 @@
 ZI_DEFINE_LAST_ERROR(elementwise)
 
 // ---------------------------------------------------------------------------------------
-// Embedding: out[n, :] = table[ids[n], :]
+// Embedding: out[n, :] = table[ids[n], :] * scale   (the product in float32; scale 1 changes nothing)
 // ---------------------------------------------------------------------------------------
 template <typename TT, typename TO>
 __global__ void embedding_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
-                                 TO* __restrict__ out, int hidden, int vocab) {
+                                 TO* __restrict__ out, int hidden, int vocab, float scale) {
     const int n = blockIdx.x;
     pdl_trigger_early();
     pdl_wait();
@@ -20,16 +20,16 @@ __global__ void embedding_kernel(const TT* __restrict__ table, const int* __rest
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);   // the host refuses ids outside the table
     const TT* src = table + (size_t)id * hidden;
     TO* dst = out + (size_t)n * hidden;
-    for (int j = threadIdx.x; j < hidden; j += blockDim.x) dst[j] = from_f32<TO>(to_f32<TT>(src[j]));
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) dst[j] = from_f32<TO>(to_f32<TT>(src[j]) * scale);
 }
 
 ZI_EXPORT int zi_embedding(const void* table, int table_dtype, const int* ids, void* out, int out_dtype,
-                           int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+                           int n_tokens, int hidden, int vocab, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hidden <= 0 || vocab <= 0) return zi_fail("embedding: hidden=%d vocab=%d must be positive", hidden, vocab);
     const int threads = hidden >= 1024 ? 256 : 128;
     ZI_DISPATCH(table_dtype, TT, ZI_DISPATCH(out_dtype, TO, {
-        zi_launch(embedding_kernel<TT, TO>, dim3(n_tokens), dim3(threads), 0, stream, (const TT*)table, ids, (TO*)out, hidden, vocab);
+        zi_launch(embedding_kernel<TT, TO>, dim3(n_tokens), dim3(threads), 0, stream, (const TT*)table, ids, (TO*)out, hidden, vocab, scale);
     }););
     return zi_check_launch("embedding");
 }

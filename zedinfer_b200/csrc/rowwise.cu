@@ -490,3 +490,171 @@ ZI_EXPORT int zi_sigmoid_mul(void* a, const void* g, int dtype, long long ldg, i
     });
     return zi_check_launch("sigmoid_mul");
 }
+
+// ---------------------------------------------------------------------------------------
+// Rotation by position of the first rot_dims entries of every query and key head, with a factor on cosines and sines,
+// then (unit_norm) every query and key head divided by its root mean square over its qk_dim entries, then the append
+// of keys and values to a paged cache whose rows are row_dim wide (row_dim >= qk_dim, v_dim; what lies past a head's own
+// entries is written as zero).
+//   x       [n_tokens, ldx]: n_q query heads and n_k key heads of qk_dim entries, then n_k value heads of v_dim entries
+//   pairing as in rotary_kernel;  the angle of pair i is float(pos) * inv_freq[i], cos and sin are multiplied by mag
+//   q_out   [n_tokens, n_q * row_dim]
+//   cache   null (queries alone: n_k is then 0), or two planes: keys after turn and norm, and the values
+// One block per token, one warp per head at a time; a head passes through the warp's stretch of shared memory, so the
+// sum of squares has one order whatever the step.
+// ---------------------------------------------------------------------------------------
+#define RN_WARPS 4
+template <typename T>
+__global__ void __launch_bounds__(RN_WARPS * 32)
+rotary_norm_kernel(const T* __restrict__ x, long long ldx, T* __restrict__ q_out, T* __restrict__ cache, const int* __restrict__ tables,
+                   const int* __restrict__ tok_seg, const int* __restrict__ pos, const float* __restrict__ inv_freq, float mag,
+                   int n_q, int n_k, int qk_dim, int v_dim, int row_dim, int rot_dims, int interleaved, int unit_norm, float eps,
+                   int page_size, int max_blocks, long long page_stride, long long kv_stride) {
+    extern __shared__ float rn_smem[];       // cos[half], sin[half], then a head per warp
+    const int n = blockIdx.x, half = rot_dims >> 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* cs = rn_smem;
+    float* head = rn_smem + rot_dims + warp * qk_dim;
+    const int p = pos[n];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf((float)p * inv_freq[i], &s, &c);
+        cs[i] = c * mag;
+        cs[half + i] = s * mag;
+    }
+    __syncthreads();
+    T* page_base = nullptr;
+    if (cache) {
+        const int seg = tok_seg ? tok_seg[n] : n;
+        const int page = tables[(size_t)seg * max_blocks + p / page_size];
+        page_base = cache + (size_t)page * page_stride + (size_t)(p % page_size) * row_dim;
+    }
+    const T* row = x + (size_t)n * ldx;
+    const int heads = n_q + (cache ? 2 * n_k : 0);
+    for (int h = warp; h < heads; h += RN_WARPS) {
+        if (h >= n_q + n_k) {                                   // a value head: copied, padded with zeros
+            const int g = h - n_q - n_k;
+            const T* src = row + (size_t)(n_q + n_k) * qk_dim + (size_t)g * v_dim;
+            T* dst = page_base + kv_stride + (size_t)g * page_size * row_dim;
+            for (int d = lane; d < row_dim; d += 32) dst[d] = d < v_dim ? src[d] : from_f32<T>(0.0f);
+            continue;
+        }
+        const T* src = row + (size_t)h * qk_dim;
+        T* dst = h < n_q ? q_out + ((size_t)n * n_q + h) * row_dim : page_base + (size_t)(h - n_q) * page_size * row_dim;
+        float ss = 0.0f;
+        for (int it = lane; it < qk_dim - half; it += 32) {
+            if (it < half) {
+                const int lo_at = interleaved ? 2 * it : it, hi_at = interleaved ? 2 * it + 1 : it + half;
+                float olo, ohi;
+                rotate_pair(to_f32<T>(src[lo_at]), to_f32<T>(src[hi_at]), cs[it], cs[half + it], &olo, &ohi);
+                head[lo_at] = olo;
+                head[hi_at] = ohi;
+            } else {
+                const int d = it - half + rot_dims;
+                head[d] = to_f32<T>(src[d]);
+            }
+        }
+        __syncwarp();
+        float r = 1.0f;
+        if (unit_norm) {
+            for (int d = lane; d < qk_dim; d += 32) ss = fmaf(head[d], head[d], ss);
+            ss = warp_sum(ss);
+            r = 1.0f / sqrtf(ss / (float)qk_dim + eps);
+        }
+        for (int d = lane; d < row_dim; d += 32) dst[d] = from_f32<T>(d < qk_dim ? head[d] * r : 0.0f);
+        __syncwarp();
+    }
+}
+
+ZI_EXPORT int zi_rotary_norm(const void* x, int dtype, long long ldx, void* q_out, void* cache, const int* tables, const int* tok_seg,
+                             const int* pos, const float* inv_freq, float mag, int n_tokens, int n_q, int n_k, int qk_dim, int v_dim,
+                             int row_dim, int rot_dims, int interleaved, int unit_norm, float eps, int page_size, int max_blocks,
+                             long long page_stride, long long kv_stride, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (qk_dim <= 0 || rot_dims < 0 || (rot_dims & 1) || rot_dims > qk_dim)
+        return zi_fail("rotary_norm: a span of %d entries does not fit a head of %d (or is odd)", rot_dims, qk_dim);
+    if (row_dim < qk_dim || (cache && row_dim < v_dim)) return zi_fail("rotary_norm: rows of %d entries cannot hold heads of %d and %d", row_dim, qk_dim, v_dim);
+    if (n_q < 0 || n_k < 0) return zi_fail("rotary_norm: bad head counts");
+    if (cache && (page_size <= 0 || max_blocks <= 0 || !tables || kv_stride == 0))
+        return zi_fail("rotary_norm: the cache append needs tables, a page size and two planes");
+    if (rot_dims > 0 && !inv_freq) return zi_fail("rotary_norm: a turned span needs its frequencies");
+    const size_t smem = (size_t)(rot_dims + RN_WARPS * qk_dim) * sizeof(float);
+    if (smem > 48 * 1024) return zi_fail("rotary_norm: heads of %d entries are too wide", qk_dim);
+    ZI_DISPATCH(dtype, T, {
+        rotary_norm_kernel<T><<<n_tokens, RN_WARPS * 32, smem, stream>>>((const T*)x, ldx, (T*)q_out, (T*)cache, tables, tok_seg, pos,
+                                                                         inv_freq, mag, n_q, n_k, qk_dim, v_dim, row_dim, rot_dims,
+                                                                         interleaved, unit_norm, eps, page_size, max_blocks, page_stride,
+                                                                         kv_stride);
+    });
+    return zi_check_launch("rotary_norm");
+}
+
+// ---------------------------------------------------------------------------------------
+// A branch's output, normed, joins the float32 residual stream:  h[n, :] += y[n, :] / sqrt(mean(y[n]^2) + eps) * w.
+// rounded (optional, of the step's type) receives the new h, which the next sublayer reads.  One block per row.
+// ---------------------------------------------------------------------------------------
+#define NA_THREADS 256
+template <typename T, typename TW>
+__global__ void __launch_bounds__(NA_THREADS)
+norm_add_kernel(float* __restrict__ h, const T* __restrict__ y, const TW* __restrict__ w, T* __restrict__ rounded, float eps, int hidden) {
+    extern __shared__ float na_row[];
+    __shared__ float scratch[32];
+    const size_t n = blockIdx.x;
+    const T* yr = y + n * hidden;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        const float v = to_f32<T>(yr[j]);
+        na_row[j] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)hidden + eps);
+    float* hr = h + n * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        const float v = hr[j] + (na_row[j] * r) * to_f32<TW>(w[j]);
+        hr[j] = v;
+        if (rounded) rounded[n * hidden + j] = from_f32<T>(v);
+    }
+}
+
+ZI_EXPORT int zi_norm_add(float* h, const void* y, int dtype, const void* w, int w_dtype, void* rounded, float eps, int rows, int hidden,
+                          cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || (size_t)hidden * sizeof(float) > 48 * 1024) return zi_fail("norm_add: hidden=%d is not supported", hidden);
+    ZI_DISPATCH(dtype, T, ZI_DISPATCH(w_dtype, TW, {
+        norm_add_kernel<T, TW><<<rows, NA_THREADS, (size_t)hidden * sizeof(float), stream>>>(h, (const T*)y, (const TW*)w, (T*)rounded, eps,
+                                                                                           hidden);
+    }););
+    return zi_check_launch("norm_add");
+}
+
+// ---------------------------------------------------------------------------------------
+// A gate on a token's own table entry:  out[n, j] = gelu_tanh(t[n, j]) * table[ids[n], col0 + j],  j < width, with
+// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), float32 inside.  Rows of t may be strided.
+// ---------------------------------------------------------------------------------------
+template <typename T, typename TT>
+__global__ void gelu_mul_rows_kernel(const T* __restrict__ t, long long ldt, const TT* __restrict__ table, long long ld_table, int col0,
+                                     const int* __restrict__ ids, int vocab, T* __restrict__ out, int width, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = i / width;
+        const int j = (int)(i - n * width);
+        int id = ids[n];
+        id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+        const float z = to_f32<T>(t[n * ldt + j]);
+        const float g = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        out[i] = from_f32<T>(g * to_f32<TT>(table[(size_t)id * ld_table + col0 + j]));
+    }
+}
+
+ZI_EXPORT int zi_gelu_mul_rows(const void* t, int dtype, long long ldt, const void* table, int table_dtype, long long ld_table, int col0,
+                               const int* ids, int vocab, void* out, int rows, int width, cudaStream_t stream) {
+    if (rows <= 0 || width <= 0) return 0;
+    if (vocab <= 0 || col0 < 0 || col0 + width > ld_table) return zi_fail("gelu_mul_rows: columns %d .. %d do not lie in a table row of %lld", col0, col0 + width, ld_table);
+    const size_t total = (size_t)rows * width;
+    const size_t want = (total + 255) / 256;
+    ZI_DISPATCH(dtype, T, ZI_DISPATCH(table_dtype, TT, {
+        gelu_mul_rows_kernel<T, TT><<<(int)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>((const T*)t, ldt, (const TT*)table, ld_table,
+                                                                                                 col0, ids, vocab, (T*)out, width, total);
+    }););
+    return zi_check_launch("gelu_mul_rows");
+}

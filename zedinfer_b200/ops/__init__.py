@@ -29,6 +29,7 @@ _attention_tcgen05 = Library("attention_tcgen05")
 _rowwise = Library("rowwise")
 _moe = Library("moe")
 _ssm = Library("ssm")
+_linrec = Library("linrec")
 SMALL_M_ROWS = 16                # the weight-streaming kernel takes up to this many rows
 
 __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", "rope_table", "gemm_smallm_rope", "can_fuse_rope_product", "silu_mul", "add", "cast",
@@ -36,10 +37,12 @@ __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", 
            "embedding_positions", "softcap", "relu2", "gated_clamp_mul", "rmsnorm_append", "linear_per_head", "route_topk",
            "moe_group", "moe_gemm", "moe_combine", "linear_gated_clamp_mul", "linear_relu2", "moe_group_padded",
            "moe_gather_rows", "gemm_tcgen05_grouped", "route", "rotary", "latent_prepare", "sigmoid_mul", "segment_bounds",
-           "causal_conv_silu", "conv_state_update", "ssm_scan", "gated_group_rmsnorm"]
+           "causal_conv_silu", "conv_state_update", "ssm_scan", "gated_group_rmsnorm", "rotary_norm", "norm_add", "gelu_mul_rows",
+           "linear_state", "group_rmsnorm_gate"]
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """``out[n] = table[ids[n]] * scale``, the product in float32."""
     need_cuda(table, ids, out)
     need_int32("ids", ids)
     need_contiguous("table", table), need_contiguous("out", out), need_contiguous("ids", ids)
@@ -47,7 +50,7 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None
     if out.shape != (n, hidden):
         raise KernelError(f"embedding: out has shape {tuple(out.shape)}, expected {(n, hidden)}")
     _elementwise.call("zi_embedding", ptr(table), c_int(dtype_code(table.dtype)), ptr(ids), ptr(out),
-                      c_int(dtype_code(out.dtype)), c_int(n), c_int(hidden), c_int(table.shape[0]), stream())
+                      c_int(dtype_code(out.dtype)), c_int(n), c_int(hidden), c_int(table.shape[0]), c_float(scale), stream())
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
@@ -566,10 +569,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
 def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                     tok_seg: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                     page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
-                    sinks: Optional[torch.Tensor] = None) -> None:
+                    sinks: Optional[torch.Tensor] = None, softcap: Optional[float] = None) -> None:
     """Causal attention of each token over its request's cache pages (general kernel).  ``kv_stride`` 0: the cache has
     one plane whose rows are keys and values at once.  ``sinks``: float32, one per query head; ``exp(sinks[h])`` joins
-    the softmax's denominator (a term without key and value)."""
+    the softmax's denominator (a term without key and value).  ``softcap`` c: a scaled score s becomes ``c tanh(s / c)``."""
     need_cuda(q, cache, out, tables, tok_seg, pos, sinks)
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != n_heads or not sinks.is_contiguous()):
         raise KernelError(f"paged_attention: sinks must be contiguous float32 with {n_heads} entries")
@@ -581,7 +584,7 @@ def paged_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tab
     _attention_generic.call("zi_paged_attention", ptr(q), ptr(cache), ptr(out), c_int(dtype_code(q.dtype)),
                             ptr(tables), ptr(tok_seg), ptr(pos), c_int(n), c_int(n_heads), c_int(n_kv_heads),
                             c_int(head_dim), c_int(page_size), c_int(tables.shape[1]), c_ll(page_stride),
-                            c_ll(kv_stride), c_int(window or 0), c_float(scale), ptr(sinks), stream())
+                            c_ll(kv_stride), c_int(window or 0), c_float(scale), ptr(sinks), c_float(softcap or 0.0), stream())
 
 
 PREFILL_TILE_ROWS = 128          # query rows per entry of a step's tile list
@@ -697,17 +700,20 @@ LATENT_TENSOR_CORES = True       # one-plane caches and sinks on the tensor-core
 
 
 def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv_heads: int, head_dim: int,
-              window: Optional[int], scale: float, sinks: Optional[torch.Tensor] = None) -> None:
+              window: Optional[int], scale: float, sinks: Optional[torch.Tensor] = None,
+              softcap: Optional[float] = None) -> None:
     """Attention of a step's tokens over the cache (``cache`` is a CallCacheView, ``ctx`` a StepContext).
 
     Picks a kernel by dtype and by the shape of the step; all of them compute the same function.
     bfloat16 with head_dim 64 or 128 runs on the tensor cores: decode-only steps, and the single tokens at the head
     of a mixed step, on the cluster decode kernel, anything else on the tcgen05 prefill kernel (pages of 8..128 tokens) or the ``mma.sync`` prefill kernel (other
     page sizes); float32 and other head sizes on the general kernel.  ``sinks`` (float32, one per query head) and a cache
-    with one plane (``cache.kv_stride`` 0, rows that are keys and values at once) are taken by every kernel.
+    with one plane (``cache.kv_stride`` 0, rows that are keys and values at once) are taken by every kernel.  ``softcap``
+    (scores through ``c tanh(s / c)``): the general kernel.
     """
     tables = ctx.tables[cache.group]
-    if q.dtype == torch.bfloat16 and head_dim in (64, 128) and (LATENT_TENSOR_CORES or (sinks is None and cache.kv_stride != 0)):
+    if (q.dtype == torch.bfloat16 and head_dim in (64, 128) and softcap is None
+            and (LATENT_TENSOR_CORES or (sinks is None and cache.kv_stride != 0))):
         n = q.shape[0]
         if ctx.decode_only and tcgen05_attention_ok(head_dim, cache.page_size):
             # in a step of single tokens, token n is segment n
@@ -739,7 +745,7 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
                               cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks)
             return
     paged_attention(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads,
-                    head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks)
+                    head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks, softcap=softcap)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
@@ -1252,3 +1258,119 @@ def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, n_gro
         raise KernelError(f"gated_group_rmsnorm: y {tuple(y.shape)}, z {tuple(z.shape)}, out {tuple(out.shape)} do not agree")
     _ssm.call("zi_gated_group_rmsnorm", ptr(y), ptr(z), c_int(dtype_code(z.dtype)), c_ll(z.stride(0)), ptr(w), c_int(dtype_code(w.dtype)),
               ptr(out), c_int(n), c_int(inner), c_int(n_groups), c_float(eps), stream())
+
+
+# ---- a turned span with a factor, unit heads and a cache whose rows are wider than a head; a normed branch into the stream;
+# ---- a gate on a token's own table entry: csrc/rowwise.cu -------------------------------------------------------------------
+def rotary_norm(x: torch.Tensor, q_out: torch.Tensor, pos: torch.Tensor, inv_freq: Optional[torch.Tensor], mag: float, n_q: int,
+                n_k: int, qk_dim: int, v_dim: int, row_dim: int, rot_dims: int, interleaved: bool, unit_eps: Optional[float],
+                cache=None, tables: Optional[torch.Tensor] = None, tok_seg: Optional[torch.Tensor] = None) -> None:
+    """Turn the first ``rot_dims`` entries of every query and key head of ``x`` (``[tokens, (n_q + n_k) * qk_dim + n_k *
+    v_dim]``, rows may be strided) by the token's position (pairing and angles as :func:`rotary`; cosines and sines times
+    ``mag``), then, with ``unit_eps``, divide every query and key head by its root mean square ``sqrt(mean + unit_eps)``.
+    Queries go to ``q_out`` (``[tokens, n_q, row_dim]``), keys and values to the two planes of ``cache`` (a CallCacheView whose
+    rows are ``row_dim`` wide); what lies past a head's own entries is written as zero.  ``cache`` None: queries alone (``x``
+    then holds no keys and values)."""
+    need_cuda(x, q_out, pos, inv_freq, tables, tok_seg)
+    need_int32("pos", pos)
+    need_contiguous("q_out", q_out)
+    n = x.shape[0]
+    if x.stride(1) != 1 or q_out.dtype != x.dtype or q_out.numel() != n * n_q * row_dim:
+        raise KernelError("rotary_norm: rows of x must be contiguous, q_out [tokens, n_q, row_dim] of x's type")
+    if rot_dims and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2 or not inv_freq.is_contiguous()):
+        raise KernelError(f"rotary_norm: inv_freq must be float32 with {rot_dims // 2} entries")
+    ct = None
+    if cache is not None:
+        ct = cache.tensor
+        if tables is None or ct.dtype != x.dtype or ct.shape[-1] != row_dim:
+            raise KernelError("rotary_norm: the cache append needs block tables and a cache of x's type with rows of row_dim")
+        need_int32("tables", tables)
+        if x.shape[1] < (n_q + n_k) * qk_dim + n_k * v_dim:
+            raise KernelError("rotary_norm: x is too narrow for its heads")
+    _rowwise.call("zi_rotary_norm", ptr(x), c_int(dtype_code(x.dtype)), c_ll(x.stride(0)), ptr(q_out), ptr(ct), ptr(tables), ptr(tok_seg),
+                  ptr(pos), ptr(inv_freq), c_float(mag), c_int(n), c_int(n_q), c_int(n_k if cache is not None else 0), c_int(qk_dim),
+                  c_int(v_dim), c_int(row_dim), c_int(rot_dims), c_int(1 if interleaved else 0), c_int(1 if unit_eps is not None else 0),
+                  c_float(unit_eps or 0.0), c_int(cache.page_size if cache is not None else 0),
+                  c_int(tables.shape[1] if tables is not None else 0), c_ll(cache.page_stride if cache is not None else 0),
+                  c_ll(cache.kv_stride if cache is not None else 0), stream())
+
+
+def norm_add(h: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, rounded: Optional[torch.Tensor] = None) -> None:
+    """``h += y / sqrt(mean(y^2) + eps) * w`` row by row, in float32 (``h`` float32 ``[rows, hidden]``); ``rounded`` (of y's
+    type) receives the new ``h``."""
+    need_cuda(h, y, w, rounded)
+    need_contiguous("h", h), need_contiguous("y", y), need_contiguous("w", w)
+    if h.dtype != torch.float32 or y.shape != h.shape or w.numel() != h.shape[1]:
+        raise KernelError(f"norm_add: h {tuple(h.shape)} float32, y {tuple(y.shape)} and w {tuple(w.shape)} do not agree")
+    if rounded is not None and (rounded.shape != h.shape or rounded.dtype != y.dtype or not rounded.is_contiguous()):
+        raise KernelError("norm_add: rounded must be contiguous, of y's type and h's shape")
+    _rowwise.call("zi_norm_add", ptr(h), ptr(y), c_int(dtype_code(y.dtype)), ptr(w), c_int(dtype_code(w.dtype)), ptr(rounded),
+                  c_float(eps), c_int(h.shape[0]), c_int(h.shape[1]), stream())
+
+
+def gelu_mul_rows(t: torch.Tensor, table: torch.Tensor, col0: int, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[n, j] = gelu_tanh(t[n, j]) * table[ids[n], col0 + j]`` (float32 inside); rows of ``t`` may be strided."""
+    need_cuda(t, table, ids, out)
+    need_int32("ids", ids)
+    need_contiguous("table", table), need_contiguous("out", out), need_contiguous("ids", ids)
+    n, width = t.shape
+    if t.stride(1) != 1 or out.shape != (n, width) or out.dtype != t.dtype or ids.numel() != n or table.dim() != 2:
+        raise KernelError(f"gelu_mul_rows: t {tuple(t.shape)}, out {tuple(out.shape)} and ids {tuple(ids.shape)} do not agree")
+    _rowwise.call("zi_gelu_mul_rows", ptr(t), c_int(dtype_code(t.dtype)), c_ll(t.stride(0)), ptr(table), c_int(dtype_code(table.dtype)),
+                  c_ll(table.shape[1]), c_int(col0), ptr(ids), c_int(table.shape[0]), ptr(out), c_int(n), c_int(width), stream())
+
+
+# ---- linear recurrences with a matrix state per head, csrc/linrec.cu ---------------------------------------------------------
+LINEAR_STATE_RULES = {"delta": 0, "decay": 1}
+
+
+def linear_state(rule: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, slots: torch.Tensor,
+                 bounds: Optional[torch.Tensor], y: torch.Tensor, n_segments: int, heads: int, kv_heads: int, dim: int, vdim: int,
+                 a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None,
+                 a_log: Optional[torch.Tensor] = None, decay: Optional[torch.Tensor] = None, act_silu: bool = False,
+                 q_scale: float = 1.0, unit_eps: float = 1e-6) -> None:
+    """Walk each segment's tokens in order through a float32 state ``S`` (``dim x vdim``) per head.
+
+    ``rule="delta"``: ``S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` with ``q`` and ``k`` made unit vectors
+    per head (``x / sqrt(sum x^2 + unit_eps)``; ``q`` also times ``q_scale``), ``beta = sigmoid(b)`` (``b [tokens, heads]``) and
+    ``g = exp(-exp(a_log) softplus(a + dt_bias))`` (``a [tokens, heads * dim]``, ``dt_bias`` float32 ``[heads * dim]``, ``a_log``
+    float32 ``[heads]``).  ``rule="decay"``: ``S <- decay_h S + k v^T; o = S^T q`` (``decay`` float32 ``[heads]``; ``q`` times
+    ``q_scale``).  ``act_silu``: q, k and v pass through SiLU first.  ``q``, ``k`` ``[tokens, kv_heads * dim]`` (head h reads
+    query/key head ``h // (heads / kv_heads)``) and ``v [tokens, heads * vdim]`` may have strided rows; ``y`` float32
+    ``[tokens, heads * vdim]``.  A request's state (``[heads, vdim, dim]``, the first entries of its slot of ``state``) is read
+    at the start and written back at the end; slot -1: zero, not written.  ``bounds`` from :func:`segment_bounds`; None:
+    segment s is token s."""
+    need_cuda(q, k, v, state, slots, bounds, y, a, b, dt_bias, a_log, decay)
+    need_int32("slots", slots)
+    need_contiguous("y", y)
+    n = q.shape[0]
+    if (q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1 or q.shape != (n, kv_heads * dim) or k.shape != q.shape
+            or v.shape != (n, heads * vdim) or not (q.dtype == k.dtype == v.dtype) or y.dtype != torch.float32
+            or y.shape != (n, heads * vdim)):
+        raise KernelError(f"linear_state: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}, y {tuple(y.shape)} do not agree")
+    for name, t, width in (("a", a, heads * dim), ("b", b, heads)):
+        if t is not None and (t.shape != (n, width) or t.stride(1) != 1 or t.dtype != q.dtype):
+            raise KernelError(f"linear_state: {name} must be [tokens, {width}] of q's type")
+    for name, t, count in (("dt_bias", dt_bias, heads * dim), ("a_log", a_log, heads), ("decay", decay, heads)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != count or not t.is_contiguous()):
+            raise KernelError(f"linear_state: {name} must be contiguous float32 with {count} entries")
+    if state.shape[1] < heads * vdim * dim:
+        raise KernelError("linear_state: the state slots are too small")
+    sp, ss = _state_args(state, 0)
+    _linrec.call("zi_linear_state", c_int(LINEAR_STATE_RULES[rule]), ptr(q), c_ll(q.stride(0)), ptr(k), c_ll(k.stride(0)), ptr(v),
+                 c_ll(v.stride(0)), ptr(a), c_ll(a.stride(0) if a is not None else 0), ptr(b), c_ll(b.stride(0) if b is not None else 0),
+                 c_int(dtype_code(q.dtype)), ptr(dt_bias), ptr(a_log), ptr(decay), sp, ss, ptr(slots), ptr(bounds), ptr(y), c_int(n),
+                 c_int(n_segments), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(1 if act_silu else 0),
+                 c_float(q_scale), c_float(unit_eps), stream())
+
+
+def group_rmsnorm_gate(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, n_groups: int, eps: float, out: torch.Tensor) -> None:
+    """``out = unit_rms(y) * w * sigmoid(z)`` with the root mean square over each of ``n_groups`` equal parts of a row and
+    ``w`` repeated along the row when it is shorter; ``y`` float32, ``z`` (rows may be strided) and ``out`` of the step's type."""
+    need_cuda(y, z, w, out)
+    need_contiguous("y", y), need_contiguous("w", w), need_contiguous("out", out)
+    n, inner = y.shape
+    if y.dtype != torch.float32 or z.shape != (n, inner) or z.stride(1) != 1 or out.shape != (n, inner) or out.dtype != z.dtype:
+        raise KernelError(f"group_rmsnorm_gate: y {tuple(y.shape)}, z {tuple(z.shape)}, out {tuple(out.shape)} do not agree")
+    _linrec.call("zi_group_rmsnorm_gate", ptr(y), ptr(z), c_int(dtype_code(z.dtype)), c_ll(z.stride(0)), ptr(w), c_int(dtype_code(w.dtype)),
+                 c_int(w.numel()), ptr(out), c_int(n), c_int(inner), c_int(n_groups), c_float(eps), stream())

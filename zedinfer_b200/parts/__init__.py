@@ -1,12 +1,13 @@
 from .base import (Block, Embedding, FeedForward, Head, Mixer, Norm, Part, PositionEncoding, ResidualStream,
                    StepContext, block_class, build_part, register_block, register_embedding, register_feed_forward,
                    register_head, register_mixer, register_norm, register_position, unregister)
-from . import attention, block, embedding, latent_attention, mlp, moe, rmsnorm, rope, ssm  # noqa: F401  (registers the built-in kinds)
+from . import attention, block, embedding, latent_attention, linear_recurrence, mlp, moe, rmsnorm, rope, ssm  # noqa: F401  (registers the built-in kinds)
 from .attention import AttentionMixer
-from .block import PreNormBlock
-from .embedding import LearnedPositionEmbedding, OutputHead, TokenEmbedding
+from .block import BranchNormBlock, PreNormBlock
+from .embedding import LearnedPositionEmbedding, OutputHead, ScaledTokenEmbedding, TokenEmbedding
+from .linear_recurrence import ChannelDeltaMixer, LightningMixer
 from .latent_attention import LatentAttentionMixer
-from .mlp import ClampedGatedMLP, GatedMLP, SquaredReluMLP
+from .mlp import ClampedGatedMLP, GatedMLP, SquaredReluMLP, TokenGatedTable
 from .moe import RoutedExperts
 from .rmsnorm import RMSNorm
 from .rope import RotaryPosition, SpanRotaryPosition
@@ -16,4 +17,5 @@ __all__ = ["Block", "Embedding", "FeedForward", "Head", "Mixer", "Norm", "Part",
            "StepContext", "block_class", "build_part", "register_block", "register_embedding",
            "register_feed_forward", "register_head", "register_mixer", "register_norm", "register_position", "unregister", "AttentionMixer", "PreNormBlock", "OutputHead",
            "TokenEmbedding", "GatedMLP", "RMSNorm", "RotaryPosition", "LearnedPositionEmbedding", "LatentAttentionMixer",
-           "ClampedGatedMLP", "SquaredReluMLP", "RoutedExperts", "SpanRotaryPosition", "Mamba2Mixer"]
+           "ClampedGatedMLP", "SquaredReluMLP", "RoutedExperts", "SpanRotaryPosition", "Mamba2Mixer", "BranchNormBlock",
+           "ScaledTokenEmbedding", "ChannelDeltaMixer", "LightningMixer", "TokenGatedTable"]

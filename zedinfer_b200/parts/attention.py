@@ -14,7 +14,13 @@ window).  Query head ``h`` reads key/value head ``h // (num_heads // num_kv_head
 Options beside the reference's form: ``value_from_key`` (there is no value projection: a token's value is its key as
 projected, before the position rule turns it; the cache still has two planes, turned keys and plain ones),
 ``unit_sink`` (the softmax's denominator holds one more term, ``exp(0)``, that has no key and no value: ``p_j = exp(s_j) /
-(1 + sum_j' exp(s_j'))``), and ``names`` (the local tensor names by role).
+(1 + sum_j' exp(s_j'))``), ``names`` (the local tensor names by role), ``softcap`` c (a scaled score s becomes ``c tanh(s /
+c)`` before the softmax), ``v_head_dim`` (value heads of another size than the query/key heads: the cache's rows and the
+heads of the query are then ``row_dim`` wide, the larger of the two sizes rounded up to a multiple of 8, and what lies past
+a head's own entries is zero, which changes no score and no output), ``shared_kv`` (the layer has no key and value
+projections: it reads the cache that another layer's call wrote, with its own queries, window and everything else) and
+``cache_window`` (the window the cache keeps pages for, where layers that read this layer's cache look further back than
+the layer itself; ``"own"``: the layer's window, None: all keys).
 """
 from __future__ import annotations
 
@@ -40,18 +46,40 @@ class AttentionMixer(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, qkv_bias: bool = True, out_bias: bool = False,
                  scale: Optional[float] = None, window: Optional[int] = None, value_from_key: bool = False,
-                 unit_sink: bool = False, names: Optional[Mapping[str, str]] = None):
+                 unit_sink: bool = False, names: Optional[Mapping[str, str]] = None, softcap: Optional[float] = None,
+                 v_head_dim: Optional[int] = None, shared_kv: bool = False, cache_window="own"):
         if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} query heads cannot share {num_kv_heads} key/value heads")
+        if softcap is not None and not softcap > 0.0:
+            raise ValueError(f"attention: softcap={softcap} must be positive (or None for no cap)")
+        if v_head_dim is not None and (v_head_dim <= 0 or position.kind != "rope_span" or value_from_key):
+            raise ValueError("attention: value heads of a size of their own need a positive size, the position rule 'rope_span' "
+                             "and a value projection")
+        if shared_kv and (value_from_key or qkv_bias):
+            raise ValueError("attention: a layer without key and value projections has neither their biases nor keys as values")
         # a rule that turns a span of the head (its own kernel) takes steps of 8; the rotate-half kernels steps of 16
         step = 8 if position.kind == "rope_span" else 16
-        if head_dim <= 0 or head_dim % step:
+        self.v_head_dim = int(v_head_dim) if v_head_dim is not None else int(head_dim)
+        # rows of the cache and heads of the query: a head's own size, or wide enough for keys and values alike
+        self.row_dim = int(head_dim) if v_head_dim is None else (max(int(head_dim), int(v_head_dim)) + 7) // 8 * 8
+        if v_head_dim is not None:
+            if head_dim <= 0 or self.row_dim > 1024:
+                raise ValueError(f"attention: head sizes {head_dim} and {v_head_dim} are not supported; rows of at most 1024 entries")
+        elif head_dim <= 0 or head_dim % step:
             raise ValueError(f"attention: head_dim={head_dim} is not supported; the kernels take head sizes "
                              f"in steps of {step} ({step}, {2 * step}, ..., 256)")
-        if head_dim > 256:
+        elif head_dim > 256:
             raise ValueError(f"attention: head_dim={head_dim} is not supported; the kernels take at most 256")
         if window is not None and window <= 0:
             raise ValueError(f"attention: window={window} must be positive (or None for all keys)")
+        if cache_window != "own" and cache_window is not None and (window is None or int(cache_window) < window):
+            raise ValueError(f"attention: cache_window={cache_window} must be at least the layer's own window {window} "
+                             "(None: all keys)")
+        self.softcap = float(softcap) if softcap is not None else None
+        self.shared_kv = bool(shared_kv)
+        # what the cache keeps: the layer's own window, or more where its readers look further back (all keys: None)
+        self.cache_window = window if cache_window == "own" else cache_window
+        self.cache_window = int(self.cache_window) if self.cache_window is not None else None
         self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
         self.head_dim, self.window = int(head_dim), (int(window) if window is not None else None)
         self.qkv_bias, self.out_bias = bool(qkv_bias), bool(out_bias)
@@ -62,8 +90,11 @@ class AttentionMixer(Mixer):
         # with the head's entries reordered at bind (SpanAsWholeRotaryPosition); keys that are also values then come out
         # of the product twice (the key rows stand in the stacked weight a second time, as the value rows), so that the
         # fused decode product and the vectorised rotation append them as they append any values.
+        if position.kind == "rope_span" and v_head_dim is None and (self.position.scaling is not None
+                                                                   or self.position.unit_rms_eps is not None):
+            raise ValueError("attention: stretched frequencies and unit heads go with v_head_dim given (the size of the value heads)")
         self._reordered = (position.kind == "rope_span" and not self.position.interleaved and self.position.offset == 0
-                           and head_dim % 16 == 0)
+                           and head_dim % 16 == 0 and v_head_dim is None)
         if self._reordered:
             self.position = build_part("position", PartSpec("rope_span_as_whole", {
                 "head_dim": head_dim, "dims": self.position.dims, "theta": self.position.theta}))
@@ -73,25 +104,33 @@ class AttentionMixer(Mixer):
                       "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias", "o_bias": "o_proj.bias"}
         self.names.update(names or {})
         self.q_dim, self.kv_dim = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        self.v_dim = self.num_kv_heads * self.v_head_dim
+        self._wide = v_head_dim is not None
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.sinks = None
 
     def cache_need(self):
-        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
+        return PagedKVNeed(self.num_kv_heads, self.row_dim, self.cache_window)
+
+    def _roles(self):
+        return ("q",) if self.shared_kv else (("q", "k") if self.value_from_key else ("q", "k", "v"))
+
+    def _width(self, role: str) -> int:
+        return {"q": self.q_dim, "k": self.kv_dim, "v": self.v_dim}[role]
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         h, nm = self.hidden_size, self.names
-        roles = ("q", "k") if self.value_from_key else ("q", "k", "v")
-        specs = {nm[r]: TensorSpec((self.q_dim if r == "q" else self.kv_dim, h)) for r in roles}
-        specs[nm["o"]] = TensorSpec((h, self.q_dim))
+        roles = self._roles()
+        specs = {nm[r]: TensorSpec((self._width(r), h)) for r in roles}
+        specs[nm["o"]] = TensorSpec((h, self.num_heads * self.v_head_dim))
         if self.qkv_bias:
-            specs.update({nm[r + "_bias"]: TensorSpec((self.q_dim if r == "q" else self.kv_dim,)) for r in roles})
+            specs.update({nm[r + "_bias"]: TensorSpec((self._width(r),)) for r in roles})
         if self.out_bias:
             specs[nm["o_bias"]] = TensorSpec((h,))
         return specs
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         nm = self.names
-        roles = ("q", "k") if self.value_from_key else ("q", "k", "v")
+        roles = self._roles()
         if self._reordered:
             order = self.position.head_order().to(tensors[nm["q"]].device)
 
@@ -117,6 +156,11 @@ class AttentionMixer(Mixer):
                 # one product, one operand type: float32 wins
                 self.w_qkv, self.b_qkv = self.w_qkv.float(), self.b_qkv.float()
         self.w_o = tensors[nm["o"]].contiguous()
+        if self.row_dim != self.v_head_dim:
+            # the attention's output has row_dim entries per head, zero past the value's own: the weight gets zero columns there
+            w_o = self.w_o.new_zeros((self.hidden_size, self.num_heads, self.row_dim))
+            w_o[:, :, :self.v_head_dim] = self.w_o.view(self.hidden_size, self.num_heads, self.v_head_dim)
+            self.w_o = w_o.view(self.hidden_size, self.num_heads * self.row_dim)
         if self.out_bias:
             self.b_o = tensors[nm["o_bias"]].contiguous()
         if self.unit_sink:
@@ -136,6 +180,23 @@ class AttentionMixer(Mixer):
         if cache.kind != "paged":
             raise RuntimeError("attention needs a paged key/value cache")
         n = x.shape[0]
+        if self.shared_kv == owns_cache:
+            raise RuntimeError("attention: a layer with key and value projections writes a cache of its own, and only a "
+                               "layer without them reads another's")
+        if self._wide or self.shared_kv:
+            # one product for whatever projections the layer has; the position rule's kernel turns, norms, pads and appends
+            proj = ctx.empty(n, self.w_qkv.shape[0])
+            ops.linear(x, self.w_qkv, self.b_qkv, proj)
+            q = ctx.empty(n, self.num_heads, self.row_dim)
+            if self._wide:
+                self.position.rotate_append(proj, q, cache, ctx, self.num_heads, self.num_kv_heads, self.head_dim,
+                                            write_kv=owns_cache, v_dim=self.v_head_dim, row_dim=self.row_dim)
+            else:
+                self.position.rotate_append(proj, q, cache, ctx, self.num_heads, self.num_kv_heads, self.head_dim, write_kv=False)
+            attn = ctx.empty(n, self.num_heads * self.row_dim)
+            ops.attention(q, cache, attn, ctx, self.num_heads, self.num_kv_heads, self.row_dim, self.window, self.scale,
+                          sinks=self.sinks, softcap=self.softcap)
+            return attn
         q = ctx.empty(n, self.num_heads, self.head_dim)
         if self.value_from_key and not self._reordered:
             qk = ctx.empty(n, self.q_dim + self.kv_dim)
@@ -150,5 +211,5 @@ class AttentionMixer(Mixer):
                                         write_kv=owns_cache)
         attn = ctx.empty(n, self.q_dim)
         ops.attention(q, cache, attn, ctx, self.num_heads, self.num_kv_heads, self.head_dim, self.window, self.scale,
-                      sinks=self.sinks)
+                      sinks=self.sinks, softcap=self.softcap)
         return attn

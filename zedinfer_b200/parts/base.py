@@ -73,6 +73,22 @@ class ResidualStream:
     h: torch.Tensor
     delta: Optional[torch.Tensor] = None
     delta_scale: float = 1.0     # the factor on ``delta`` when a norm folds it in: ``h += delta_scale * delta`` (float32)
+    # ``h`` rounded to the step's type, where the kernel that last changed ``h`` made that copy on its way (arrangements
+    # whose sublayers read the stream itself); whoever changes ``h`` otherwise sets it to None
+    rounded: Optional[torch.Tensor] = None
+
+    def as_input(self, ctx: "StepContext") -> torch.Tensor:
+        """The stream as a sublayer's input: ``h`` itself in a float32 step, else its rounded copy (made here if nobody
+        has made it yet).  Nothing may be pending in ``delta``."""
+        if self.delta is not None:
+            raise RuntimeError("a branch output is still pending: fold it into the stream first")
+        if ctx.dtype == torch.float32:
+            return self.h
+        if self.rounded is None:
+            from .. import ops
+            self.rounded = ctx.empty(*self.h.shape)
+            ops.cast(self.h, self.rounded)
+        return self.rounded
 
 
 # ---- part interfaces ------------------------------------------------------------------------
@@ -101,6 +117,11 @@ class Norm(Part):
         With ``row_idx`` only those rows are produced and the stream is left as it is.
         """
         raise NotImplementedError
+
+    def forward_branch(self, stream: ResidualStream, y: torch.Tensor, ctx: "StepContext") -> None:
+        """Optional, for arrangements that norm a branch's *output*: ``stream.h += norm(y)`` in float32, leaving the
+        rounded copy of the new ``h`` in ``stream.rounded`` where the step's type is not float32."""
+        raise NotImplementedError(f"{type(self).__name__} cannot norm a branch's output into the stream")
 
 
 class Embedding(Part):

@@ -39,3 +39,36 @@ class PreNormBlock(Block):
         normed2 = ctx.empty(n, hidden)
         self.norms["norm2"].forward_residual(stream, normed2)
         stream.delta = self.ffn.forward_for_residual(normed2, ctx)
+
+
+@register_block("branch_norm")
+class BranchNormBlock(Block):
+    """The norm sits on each branch's *output*, and the branches read the stream itself:
+
+        h = h + norm1(mixer(h));  h = h + norm2(ffn(h));  h = h + norm_side(side(h))
+
+    ``ffn`` with ``norm2`` and ``side`` with ``norm_side`` are optional.  ``side`` is a feed-forward part (it may read
+    the step's token ids, e.g. a gate on a per-token table entry).  The sums are float32; in a bfloat16 step the kernel
+    that adds a normed branch also leaves the rounded stream for the next branch to read."""
+    capture_safe = True
+
+    def __init__(self, parts):
+        super().__init__(parts)
+        have = self.parts()
+        need = ["mixer", "norm1"]
+        for branch, norm in (("ffn", "norm2"), ("side", "norm_side")):
+            if branch in have or norm in have:
+                need += [branch, norm]
+        missing = [role for role in need if role not in have]
+        if missing:
+            raise ValueError(f"the branch_norm arrangement needs the parts {missing} as well")
+        self.side = have.get("side")
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, caches: Mapping[str, CallCacheView],
+                owns_cache: bool) -> None:
+        y = self.mixer.forward(stream.as_input(ctx), ctx, caches["mixer"], owns_cache)
+        self.norms["norm1"].forward_branch(stream, y, ctx)
+        if self.ffn is not None:
+            self.norms["norm2"].forward_branch(stream, self.ffn.forward(stream.as_input(ctx), ctx), ctx)
+        if self.side is not None:
+            self.norms["norm_side"].forward_branch(stream, self.side.forward(stream.as_input(ctx), ctx), ctx)

@@ -40,6 +40,42 @@ class TokenEmbedding(Embedding):
         return self.table
 
 
+@register_embedding("scaled_token_embedding")
+class ScaledTokenEmbedding(TokenEmbedding):
+    """``hidden[n] = table[ids[n]] * scale`` (the product in float32); a tied head reads the table itself, without the
+    scale.  ``token_tables`` names further tables with a row per token of the vocabulary (``{key: (tensor name, width)}``)
+    that parts of the layers read by the step's token ids: the embedding loads them and leaves each under
+    ``ctx.step_cache[("token_table", key)]`` for the step."""
+    capture_safe = True
+
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, name: str = "embed_tokens.weight",
+                 token_tables: Optional[Mapping[str, tuple]] = None):
+        super().__init__(vocab_size, hidden_size, name)
+        self.scale = float(scale)
+        self.token_tables = {key: (str(tname), int(width)) for key, (tname, width) in (token_tables or {}).items()}
+        for key, (tname, width) in self.token_tables.items():
+            if width <= 0:
+                raise ValueError(f"scaled_token_embedding: the table {key!r} needs a positive width, got {width}")
+        self.tables: Dict[str, torch.Tensor] = {}
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        specs = super().tensor_specs()
+        specs.update({tname: TensorSpec((self.vocab_size, width)) for tname, width in self.token_tables.values()})
+        return specs
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        super().bind(tensors)
+        self.tables = {key: tensors[tname].contiguous() for key, (tname, _) in self.token_tables.items()}
+
+    def forward(self, ids: torch.Tensor, out: torch.Tensor) -> None:
+        ops.embedding(self.table, ids, out, scale=self.scale)
+
+    def forward_step(self, ctx, out: torch.Tensor) -> None:
+        self.forward(ctx.token_ids, out)
+        for key, table in self.tables.items():
+            ctx.step_cache[("token_table", key)] = table
+
+
 @register_embedding("learned_position_embedding")
 class LearnedPositionEmbedding(Embedding):
     """Token table plus a table of learned absolute positions (not scaled), added in float32."""

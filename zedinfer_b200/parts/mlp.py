@@ -22,32 +22,42 @@ def _stack(tensors):
 class GatedMLP(FeedForward):
     capture_safe = True
 
-    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", bias: bool = False,
+                 names: Optional[Mapping[str, str]] = None):
+        """``names``: the local tensor names of the three weights by role (``gate``, ``up``, ``down``); a bias is the
+        weight's name with ``.weight`` replaced by ``.bias``."""
         if activation != "silu":
             raise ValueError(f"gated_mlp: activation {activation!r} is not supported (only 'silu')")
         if hidden_size <= 0 or intermediate_size <= 0:
             raise ValueError("gated_mlp: sizes must be positive")
         self.hidden_size, self.intermediate_size, self.bias = int(hidden_size), int(intermediate_size), bool(bias)
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
+        self.names.update(names or {})
+        if self.bias and not all(n.endswith(".weight") for n in self.names.values()):
+            raise ValueError("gated_mlp: biases are named after weights that end in '.weight'")
         self.w_gate_up: Optional[torch.Tensor] = None
         self.b_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
         self.b_down: Optional[torch.Tensor] = None
 
+    def _bias_name(self, role: str) -> str:
+        return self.names[role][:-len("weight")] + "bias"
+
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        h, i = self.hidden_size, self.intermediate_size
-        specs = {"gate_proj.weight": TensorSpec((i, h)), "up_proj.weight": TensorSpec((i, h)),
-                 "down_proj.weight": TensorSpec((h, i))}
+        h, i, nm = self.hidden_size, self.intermediate_size, self.names
+        specs = {nm["gate"]: TensorSpec((i, h)), nm["up"]: TensorSpec((i, h)), nm["down"]: TensorSpec((h, i))}
         if self.bias:
-            specs.update({"gate_proj.bias": TensorSpec((i,)), "up_proj.bias": TensorSpec((i,)),
-                          "down_proj.bias": TensorSpec((h,))})
+            specs.update({self._bias_name("gate"): TensorSpec((i,)), self._bias_name("up"): TensorSpec((i,)),
+                          self._bias_name("down"): TensorSpec((h,))})
         return specs
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.w_gate_up = _stack([tensors["gate_proj.weight"], tensors["up_proj.weight"]])
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        nm = self.names
+        self.w_gate_up = _stack([tensors[nm["gate"]], tensors[nm["up"]]])
+        self.w_down = tensors[nm["down"]].contiguous()
         if self.bias:
-            self.b_gate_up = _stack([tensors["gate_proj.bias"], tensors["up_proj.bias"]])
-            self.b_down = tensors["down_proj.bias"].contiguous()
+            self.b_gate_up = _stack([tensors[self._bias_name("gate")], tensors[self._bias_name("up")]])
+            self.b_down = tensors[self._bias_name("down")].contiguous()
 
     def _activation(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         act = ctx.empty(x.shape[0], self.intermediate_size)
@@ -136,3 +146,40 @@ class ClampedGatedMLP(FeedForward):
 
     def forward_for_residual(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         return ops.linear_for_residual(self._activation(x, ctx), self.w_down, None)
+
+
+@register_feed_forward("token_gated_table")
+class TokenGatedTable(FeedForward):
+    """A token's own table entry, gated by the stream: ``proj(gelu_tanh(gate(x)) * table[token, col0 : col0 + dim])``, no
+    biases.  The table has a row per token of the vocabulary and is the embedding's to load (``scaled_token_embedding``'s
+    ``token_tables``); this part finds it under ``ctx.step_cache[("token_table", table)]`` and reads ``dim`` columns from
+    ``col0`` on (a layer's share of a table that all layers divide among themselves)."""
+    capture_safe = True
+
+    def __init__(self, hidden_size: int, dim: int, table: str, col0: int = 0, gate_name: str = "gate", proj_name: str = "proj"):
+        if hidden_size <= 0 or dim <= 0 or col0 < 0:
+            raise ValueError("token_gated_table: sizes must be positive")
+        self.hidden_size, self.dim, self.table, self.col0 = int(hidden_size), int(dim), str(table), int(col0)
+        self.gate_name, self.proj_name = gate_name, proj_name
+        self.w_gate: Optional[torch.Tensor] = None
+        self.w_proj: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.gate_name: TensorSpec((self.dim, self.hidden_size)), self.proj_name: TensorSpec((self.hidden_size, self.dim))}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_gate = tensors[self.gate_name].contiguous()
+        self.w_proj = tensors[self.proj_name].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        table = ctx.step_cache.get(("token_table", self.table))
+        if table is None:
+            raise RuntimeError(f"token_gated_table: the model's embedding has left no table {self.table!r} for this step")
+        n = x.shape[0]
+        t = ctx.empty(n, self.dim)
+        ops.linear(x, self.w_gate, None, t)
+        g = ctx.empty(n, self.dim)
+        ops.gelu_mul_rows(t, table, self.col0, ctx.token_ids, g)
+        out = ctx.empty(n, self.hidden_size)
+        ops.linear(g, self.w_proj, None, out)
+        return out

@@ -9,7 +9,7 @@ import torch
 
 from .. import ops
 from ..weights.loader import TensorSpec
-from .base import Norm, ResidualStream, register_norm
+from .base import Norm, ResidualStream, StepContext, register_norm
 
 
 @register_norm("rmsnorm")
@@ -41,4 +41,12 @@ class RMSNorm(Norm):
         ops.add_rmsnorm(stream.h, stream.delta, self.weight, self.eps, out, row_idx=row_idx,
                         write_residual=row_idx is None, delta_scale=stream.delta_scale)
         if row_idx is None:
+            if stream.delta is not None:
+                stream.rounded = None           # h has changed
             stream.delta = None
+
+    def forward_branch(self, stream: ResidualStream, y: torch.Tensor, ctx: StepContext) -> None:
+        """``h += y / sqrt(mean(y^2) + eps) * w`` (float32), and the rounded copy of the new ``h`` for the next sublayer."""
+        rounded = None if ctx.dtype == torch.float32 else ctx.empty(*stream.h.shape)
+        ops.norm_add(stream.h, y, self.weight, self.eps, rounded)
+        stream.rounded = rounded

@@ -10,7 +10,8 @@ that rotates also appends k and v to the cache pages of each token's request.
 """
 from __future__ import annotations
 
-from typing import Optional
+import math
+from typing import Mapping, Optional
 
 import torch
 
@@ -93,19 +94,57 @@ class SpanRotaryPosition(PositionEncoding):
     capture_safe = True
     takes_value_from_key = True
 
-    def __init__(self, head_dim: int, dims: int, theta: float, interleaved: bool = False, offset: int = 0):
-        if head_dim <= 0 or dims <= 0 or dims % 2 or offset < 0 or offset + dims > head_dim:
+    def __init__(self, head_dim: int, dims: int, theta: float, interleaved: bool = False, offset: int = 0,
+                 scaling: Optional[Mapping[str, float]] = None, unit_rms_eps: Optional[float] = None):
+        """``scaling`` (``factor``, ``original``, ``fast``, ``slow``): the frequencies are stretched for contexts longer than
+        ``original`` positions, pair by pair (see :meth:`inverse_frequencies`), and cosines and sines are multiplied by
+        ``0.1 ln(factor) + 1``.  ``unit_rms_eps``: after the turn every query and key head is divided by its root mean square
+        ``sqrt(mean(x^2) + unit_rms_eps)``.  Either option, a cache whose rows are wider than a head or a value size of its
+        own takes the kernel ``ops.rotary_norm`` (span at the start of the head); ``dims`` may then be 0 (nothing turns)."""
+        plain = scaling is None and unit_rms_eps is None
+        if head_dim <= 0 or dims < 0 or (dims == 0 and plain) or dims % 2 or offset < 0 or offset + dims > head_dim:
             raise ValueError(f"rope_span: a span of {dims} entries from {offset} must be even and fit a head of {head_dim}")
         if not theta > 0.0:
             raise ValueError(f"rope_span: theta={theta} must be positive")
+        if not plain and offset:
+            raise ValueError("rope_span: stretched frequencies and unit heads need the span at the start of the head")
+        if unit_rms_eps is not None and not unit_rms_eps > 0.0:
+            raise ValueError(f"rope_span: unit_rms_eps={unit_rms_eps} must be positive")
         self.head_dim, self.dims, self.theta = int(head_dim), int(dims), float(theta)
         self.interleaved, self.offset = bool(interleaved), int(offset)
+        self.unit_rms_eps = float(unit_rms_eps) if unit_rms_eps is not None else None
+        self.scaling = None
+        self.magnitude = 1.0
+        if scaling is not None:
+            missing = [k for k in ("factor", "original", "fast", "slow") if k not in scaling]
+            if missing:
+                raise ValueError(f"rope_span: scaling lacks {missing}")
+            self.scaling = {k: float(scaling[k]) for k in ("factor", "original", "fast", "slow")}
+            if not (self.scaling["factor"] > 0.0 and self.scaling["original"] > 0.0 and self.scaling["fast"] > 0.0
+                    and self.scaling["slow"] > 0.0 and self.theta != 1.0):
+                raise ValueError(f"rope_span: scaling={dict(scaling)} must be positive throughout (and theta differ from 1)")
+            self.magnitude = 0.1 * math.log(self.scaling["factor"]) + 1.0
         self._inv_freq: Optional[torch.Tensor] = None
 
     def inverse_frequencies(self) -> torch.Tensor:
-        """float32 table on the CPU: 1 / powf(theta, float(2i) / float(dims))."""
-        expo = torch.arange(0, self.dims, 2, dtype=torch.float32) / torch.tensor(float(self.dims), dtype=torch.float32)
-        return 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float32), expo)
+        """float32 table on the CPU: ``f_i = theta^(-2i / dims)``.  With ``scaling``: let ``D(n) = dims ln(original / (2 pi
+        n)) / (2 ln theta)`` be the pair that makes n full turns over ``original`` positions, ``lo = max(floor(D(fast)), 0)``,
+        ``hi = min(ceil(D(slow)), dims - 1)`` and ``m_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``; the table holds ``f_i
+        / factor * m_i + f_i (1 - m_i)``: pairs below ``lo`` keep their frequency, pairs above ``hi`` turn ``factor`` times
+        slower.  Formed in float64 and rounded once."""
+        i = torch.arange(0, self.dims // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * i / max(self.dims, 1))
+        if self.scaling is not None:
+            sc = self.scaling
+
+            def pair_of(turns: float) -> float:
+                return self.dims * math.log(sc["original"] / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+
+            lo = max(math.floor(pair_of(sc["fast"])), 0)
+            hi = min(math.ceil(pair_of(sc["slow"])), self.dims - 1)
+            ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / sc["factor"] * ramp + f * (1.0 - ramp)
+        return f.to(torch.float32)
 
     def table(self, device: torch.device) -> torch.Tensor:
         if self._inv_freq is None or self._inv_freq.device != device:
@@ -113,9 +152,22 @@ class SpanRotaryPosition(PositionEncoding):
         return self._inv_freq
 
     def rotate_append(self, qkv: torch.Tensor, q_out: torch.Tensor, cache: CallCacheView, ctx: StepContext,
-                      n_heads: int, n_kv_heads: int, head_dim: int, write_kv: bool, value_from_key: bool = False) -> None:
+                      n_heads: int, n_kv_heads: int, head_dim: int, write_kv: bool, value_from_key: bool = False,
+                      v_dim: Optional[int] = None, row_dim: Optional[int] = None) -> None:
+        """``v_dim``: the value heads' size where it differs from ``head_dim``; ``row_dim``: the width of the cache's rows
+        and of the heads of ``q_out`` where that is more than a head (the rest is written as zero)."""
         if head_dim != self.head_dim:
             raise ValueError(f"rope_span was built for head_dim={self.head_dim}, the mixer has {head_dim}")
+        v_dim = head_dim if v_dim is None else v_dim
+        row_dim = head_dim if row_dim is None else row_dim
+        if self.scaling is not None or self.unit_rms_eps is not None or v_dim != head_dim or row_dim != head_dim or not self.dims:
+            if value_from_key:
+                raise ValueError("rope_span: unturned keys as values go with the plain span only")
+            ops.rotary_norm(qkv, q_out, ctx.positions, self.table(qkv.device) if self.dims else None, self.magnitude, n_heads,
+                            n_kv_heads, head_dim, v_dim, row_dim, self.dims, self.interleaved, self.unit_rms_eps,
+                            cache=cache if write_kv else None, tables=ctx.tables[cache.group] if write_kv else None,
+                            tok_seg=ctx.tok_seg if write_kv else None)
+            return
         if not write_kv:
             ops.rotary(qkv, q_out, ctx.positions, self.table(qkv.device), n_heads, 0, head_dim, self.offset, self.dims,
                        self.interleaved)
