@@ -349,6 +349,34 @@ def gibalorn_config(width, heads, layers, vocab, experts, top, expert_ff, dim=12
             "layers": out, "loop": None}
 
 
+def kevatar_config(width, heads, ff, window, layers, vocab, dim=128, **_):
+    """The Kevatar design at the same width, layers, heads, head size, window, vocabulary and feed-forward as the Qwen2
+    configuration beside it (both have the gated SiLU feed-forward of three matrices): its mixers in turn (windowed attention
+    with keys of its own, the delta rule, lightning, windowed attention on the first layer's keys), half of every head
+    turned with stretched frequencies, scores capped, recurrent heads of 128 x 128 with low ranks of 64, four taps, and a
+    per-token table of 64 columns a layer."""
+    kv = 2 if heads <= 12 else 4
+    rot = {"base": 1000000.0, "dims": dim // 2, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+    out = []
+    for i in range(layers):
+        kind = i % 4
+        if kind in (0, 3):
+            m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": window}, "rot": rot,
+                 "scale": dim ** -0.5, "softcap": 30.0}
+            if kind == 3:
+                m["kv_from"] = i - 3
+            out.append({"type": "attention", "mixer": m})
+        elif kind == 1:
+            out.append({"type": "channel_delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": 4,
+                                                           "decay_rank": 64, "gate_rank": 64}})
+        else:
+            out.append({"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": dim,
+                                                       "decay": [1.0 - 2.0 ** -(2 + 6 * h / max(1, heads - 1)) for h in range(heads)]}})
+        out[-1]["mlp"] = {"kind": "dense", "ff": (2 * ff // 3 + 7) // 8 * 8}
+    return {"architecture": "Kevatar", "vocab": vocab, "width": width, "max_positions": CONTEXT, "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(width) ** 0.5}, "token_side": {"dim": 64}, "layers": out}
+
+
 def measure_design(cfg, vocab, batch, steps, warmup):
     """Prefill of PROMPT_LEN tokens in one step and decode of `batch` requests through the captured greedy step."""
     import torch
@@ -398,13 +426,22 @@ def design_comparison(args):
     import torch  # noqa: F401
     from zedinfer_b200.csrc import build
     from zedinfer_b200.engine.core import EngineCore
-    build.compile_all(EngineCore.kernel_libraries("bfloat16") + ["gemm_tcgen05", "attention_tcgen05", "rowwise", "moe", "ssm"], verbose=False)
+    build.compile_all(EngineCore.kernel_libraries("bfloat16") + ["gemm_tcgen05", "attention_tcgen05", "rowwise", "moe", "ssm", "linrec"],
+                      verbose=False)
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     clocks = ClockSampler()
     clocks.start()
     rows = []
     for name, size in DESIGN_SIZES.items():
         q = {k: size[k] for k in ("width", "heads", "ff", "window", "layers", "vocab")}
+        if args.designs == "kevatar":
+            # the design beside the model it is closest to: dense feed-forward, grouped heads, a window
+            qwen = measure_design(qwen2_config_like(**q), size["vocab"], args.batch, steps, warmup)
+            kev = measure_design(kevatar_config(**q), size["vocab"], args.batch, steps, warmup)
+            rows.append({"size": name, "shape": q, "kevatar": kev, "qwen2_equal_size": qwen,
+                         "prefill_ratio": round(kev["prefill_tokens_per_s"] / qwen["prefill_tokens_per_s"], 3),
+                         "decode_ratio": round(kev["decode_tokens_per_s"] / qwen["decode_tokens_per_s"], 3)})
+            continue
         base = measure_design(baselix_config(**size), size["vocab"], args.batch, steps, warmup)
         qwen = measure_design(qwen2_config_like(**q), size["vocab"], args.batch, steps, warmup)
         row = {"size": name, "shape": size, "baselix": base, "qwen2_equal_size": qwen,
@@ -511,10 +548,10 @@ def main():
     ap.add_argument("--layers", type=int, default=MODEL_1P5B["num_hidden_layers"],
                     help="fewer layers than the model has (same layer sizes), where memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
-    ap.add_argument("--designs", nargs="?", const="baselix", default=None, choices=["baselix", "gibalorn"],
+    ap.add_argument("--designs", nargs="?", const="baselix", default=None, choices=["baselix", "gibalorn", "kevatar"],
                     help="instead of the default workload: prefill and decode of the Baselix design at layer sizes of real "
                          "models (random weights) beside Qwen2 at equal size; '--designs gibalorn' also runs the Gibalorn "
-                         "design at those sizes")
+                         "design at those sizes; '--designs kevatar' runs the Kevatar design beside Qwen2 alone")
     args = ap.parse_args()
 
     if args.impl == "reference":

@@ -504,6 +504,81 @@ def test_prefill_attention_tensor_cores(nh, nkv, hd, ps, window, kernel):
         i += cnt
 
 
+def capped_attention_rows(q, k, v, positions, scale, window, cap):
+    """As :func:`plain_attention_rows`, every scaled score s going through ``cap * tanh(s / cap)`` first."""
+    out = torch.zeros_like(q)
+    nh, nkv = q.shape[1], k.shape[1]
+    pos = torch.tensor(list(positions))
+    keys = torch.arange(k.shape[0])
+    seen = keys[None, :] <= pos[:, None]
+    if window:
+        seen &= keys[None, :] > pos[:, None] - window
+    for h in range(nh):
+        kvh = h // (nh // nkv)
+        s = cap * torch.tanh((q[:, h] @ k[:, kvh].t()) * scale / cap)
+        out[:, h] = torch.softmax(s.masked_fill(~seen, float("-inf")), dim=1) @ v[:, kvh]
+    return out
+
+
+@pytest.mark.parametrize("kernel", ["cp_async", "tma", "mma", "tcgen05", "general"])
+@pytest.mark.parametrize("nh,nkv,hd,ps,window,cap", [(6, 2, 128, 16, None, 2.0), (4, 4, 64, 8, 90, 1.0), (5, 1, 128, 32, 300, 30.0)])
+def test_tensor_core_attention_with_a_score_cap(nh, nkv, hd, ps, window, cap, kernel):
+    """Queries three times as long as usual, so that plain scores spread far beyond the cap and an uncapped softmax
+    would be all but one-hot: decode kernels on the requests' last tokens, prefill kernels on portions, each against the
+    float32 formula.  Without the cap the same inputs must differ from it (the test's own premise)."""
+    from zedinfer_b200 import ops
+    t = torch.bfloat16
+    lens = [1, 130, 257, 700, 64, 1500]
+    pool, view, tables, ks, vs, page_stride, kv_stride = build_cache(len(lens), lens, nkv, hd, ps, t, seed=11)
+    g = torch.Generator().manual_seed(12)
+    scale = 1.0 / math.sqrt(hd)
+    if kernel in ("cp_async", "tma", "general"):
+        portions = [(r, l - 1, 1) for r, l in enumerate(lens)]
+    else:
+        portions = [(0, 0, 1), (1, 0, 130), (2, 200, 57), (3, 130, 570), (5, 1363, 137)]
+    n = sum(c for _, _, c in portions)
+    q = (torch.randn(n, nh, hd, generator=g) * 3.0).to(t)
+    pos = [p0 + i for _, p0, c in portions for i in range(c)]
+    seg = [si for si, (_, _, c) in enumerate(portions) for _ in range(c)]
+    rows = ops.PREFILL_TILE_ROWS
+    tiles, at = [], 0
+    for si, (_, _, c) in enumerate(portions):
+        tiles += [(at + q0, min(rows, c - q0), si) for q0 in range(0, c, rows)]
+        at += c
+    seg_tables = torch.stack([tables[r] for r, _, _ in portions])
+    if window:
+        seg_tables = release_behind_window(seg_tables, [p0 for _, p0, _ in portions], window, ps, pool.shape[0] - 1)
+    qd = q.to(dev())
+    pos_d = torch.tensor(pos, dtype=torch.int32, device=dev())
+    seg_d = torch.tensor(seg, dtype=torch.int32, device=dev())
+    tiles_d = torch.tensor(tiles, dtype=torch.int32, device=dev())
+
+    def run(softcap):
+        out = torch.full((n, nh * hd), float("nan"), dtype=t, device=dev())
+        if kernel == "general":
+            ops.paged_attention(qd, view, out, seg_tables, seg_d, pos_d, nh, nkv, hd, ps, page_stride, kv_stride, window, scale, softcap=softcap)
+        elif kernel in ("cp_async", "tma"):
+            fn = ops.decode_attention if kernel == "cp_async" else ops.decode_attention_tma
+            fn(qd, view, out, seg_tables, seg_d, pos_d, nh, nkv, hd, ps, page_stride, kv_stride, window, scale, softcap=softcap)
+        else:
+            fn = ops.prefill_attention if kernel == "mma" else ops.prefill_attention_tcgen05
+            fn(qd, view, out, seg_tables, tiles_d, pos_d, nh, nkv, hd, ps, page_stride, kv_stride, window, scale, softcap=softcap)
+        torch.cuda.synchronize()
+        assert ops.tcgen05_status(dev()) == 0
+        return out.float().cpu().view(n, nh, hd)
+
+    got, bare = run(cap), run(None)
+    qf = q.float()
+    i, worst, apart = 0, 0.0, 0.0
+    for r, p0, c in portions:
+        ref = capped_attention_rows(qf[i:i + c], ks[r], vs[r], list(range(p0, p0 + c)), scale, window, cap)
+        worst = max(worst, float((got[i:i + c] - ref).abs().max()))
+        apart = max(apart, float((bare[i:i + c] - ref).abs().max()))
+        i += c
+    assert worst < 2e-2, worst
+    assert cap >= 30.0 or apart > 0.2, apart
+
+
 @pytest.mark.parametrize("rows,n,k", [(17, 1536, 8960), (64, 1536, 8960), (256, 896, 4864), (40, 3584, 18944)])
 def test_product_as_partial_sums_folded_by_the_norm(rows, n, k):
     """A product whose result goes into the residual stream may come as float32 sums over four ranges of K; the norm

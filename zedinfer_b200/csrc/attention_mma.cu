@@ -146,6 +146,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Score cap c: a scaled score becomes c tanh(s scale / c).  The kernels take cap_in = scale / c (0: no cap) and, with a cap,
+// scale2 = c log2(e): the raw dot products are replaced by tanh(s cap_in) before the softmax step, which multiplies by
+// scale2 as ever.  tanh(y) = 1 - 2 / (1 + exp(2 y)): one ex2 and one reciprocal, right at both ends (exp2 = inf or 0).
+__device__ __forceinline__ float capped_tanh(float y) {
+    return 1.0f - __fdividef(2.0f, 1.0f + fast_exp2(y * 2.8853900817779268f));
+}
+template <int NKT>
+__device__ __forceinline__ void cap_scores(float (&S)[NKT][4], float cap_in) {
+    if (cap_in > 0.0f) {
+#pragma unroll
+        for (int nt = 0; nt < NKT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) S[nt][e] = capped_tanh(S[nt][e] * cap_in);
+    }
+}
+
 // Online softmax step on a warp's score tile.  Thread holds rows g = lane/4 (values [0],[1]) and g+8
 // ([2],[3]) at keys key0 + nt*8 + (lane%4)*2 + {0,1}.  lo / hi: first / last key each row may see.
 // S comes in as raw dot products and leaves as probabilities relative to the running maximum; m is kept
@@ -214,7 +230,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
                         const int* __restrict__ tables, const int* __restrict__ tok_seg,
                         const int* __restrict__ pos, int n_heads, int n_kv_heads, int q_blocks, int page_size,
                         int page_shift, int max_blocks, long long page_stride, long long kv_stride, int window,
-                        float scale2, const float* __restrict__ sinks) {
+                        float scale2, const float* __restrict__ sinks, float cap_in) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -285,6 +301,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cac
         if (key0 <= P && key0 + 15 >= lo) {                   // this warp's 16 keys hold something visible
             float S[2][4];
             qk_scores<HD, 2>(S, qf, sK, warp * 16, lane);
+            cap_scores<2>(S, cap_in);
             softmax_step<HD, 2>(S, O, m, l, key0, lane, lo, P, lo, P, scale2);
             pv_accumulate<HD, 2>(O, S, sV, warp * 16, lane);
         }
@@ -467,7 +484,8 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
                             const int* __restrict__ tables, const int* __restrict__ tok_seg, const int* __restrict__ pos,
                             int* __restrict__ status, int n_heads, int n_kv_heads, int q_blocks, int page_size,
                             int box_rows, int max_blocks, int window, float scale2, int n_splits, int min_split_tiles,
-                            float* __restrict__ part, int kv_box, const float* __restrict__ sinks, int one_plane) {
+                            float* __restrict__ part, int kv_box, const float* __restrict__ sinks, int one_plane,
+                            float cap_in) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -600,6 +618,7 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap map_kv, const bf
         const int key0 = (t_lo + first + i * CL * 4) * DT_KEYS;
         float S[DT_KEYS / 8][4];
         qk_scores_tma<HD, DT_KEYS / 8>(S, qf, sK, lane);
+        cap_scores<DT_KEYS / 8>(S, cap_in);
         if (key0 >= lo && key0 + DT_KEYS - 1 <= P) softmax_step<HD, DT_KEYS / 8, false>(S, O, m, l, key0, lane, lo, P, lo, P, scale2);
         else softmax_step<HD, DT_KEYS / 8, true>(S, O, m, l, key0, lane, lo, P, lo, P, scale2);
         pv_accumulate_tma<HD, DT_KEYS / 8>(O, S, sV, lane);
@@ -706,7 +725,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ ca
                          const int* __restrict__ tables, const int* __restrict__ tiles, const int* __restrict__ pos,
                          int n_heads, int n_kv_heads, int page_size, int page_shift, int max_blocks,
                          long long page_stride, long long kv_stride, int window, float scale2,
-                         const float* __restrict__ sinks) {
+                         const float* __restrict__ sinks, float cap_in) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     constexpr int TILE_BYTES = TILE_KEYS * HD * 2;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -777,6 +796,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ ca
         if (w_rows > 0 && key0 <= w_hi && key0 + TILE_KEYS - 1 >= w_lo) {
             float S[8][4];
             qk_scores<HD, 8>(S, qf, sK, 0, lane);
+            cap_scores<8>(S, cap_in);
             // every existing row of the warp sees the whole tile: rows sit at p0 + warp*16 .. w_hi
             const bool full = w_rows >= 16 && key0 + TILE_KEYS - 1 <= p0 + warp * 16 &&
                               (window <= 0 || key0 >= w_hi - window + 1);
@@ -854,14 +874,14 @@ static cudaError_t launch_cluster(K kernel, dim3 grid, dim3 block, size_t smem, 
 ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, const int* tables, const int* tok_seg,
                                   const int* pos, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                   int page_size, int max_blocks, long long page_stride, long long kv_stride,
-                                  int window, float scale, const float* sinks, cudaStream_t stream) {
+                                  int window, float scale, const float* sinks, float softcap, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (check_common("decode_attention", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
     if (n_tokens > 65535) return zi_fail("decode_attention: %d tokens are more than one launch takes (65535)", n_tokens);
     const int group = n_heads / n_kv_heads, q_blocks = (group + 15) / 16;
     if (n_kv_heads * q_blocks > 65535) return zi_fail("decode_attention: too many head blocks for one launch");
     dim3 grid(DEC_CLUSTER, n_kv_heads * q_blocks, n_tokens);
-    const float scale2 = scale * LOG2E;
+    const float scale2 = (softcap > 0.0f ? softcap : scale) * LOG2E, cap_in = softcap > 0.0f ? scale / softcap : 0.0f;
     const int shift = page_shift_of(page_size);
     cudaError_t e;
     if (head_dim == 128) {
@@ -869,13 +889,13 @@ ZI_EXPORT int zi_decode_attention(const void* q, const void* cache, void* out, c
         if (set_smem(decode_attention_kernel<128>, smem, "decode_attention")) return 1;
         e = launch_cluster(decode_attention_kernel<128>, grid, dim3(ATT_THREADS), smem, stream,
                            (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tok_seg, pos, n_heads, n_kv_heads,
-                           q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2, sinks);
+                           q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2, sinks, cap_in);
     } else {
         const size_t smem = 16 * 64 * 2 + DEC_STAGES * 2 * TILE_KEYS * 64 * 2 + (32 + 16 * (64 + 8)) * 4;
         if (set_smem(decode_attention_kernel<64>, smem, "decode_attention")) return 1;
         e = launch_cluster(decode_attention_kernel<64>, grid, dim3(ATT_THREADS), smem, stream,
                            (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tok_seg, pos, n_heads, n_kv_heads,
-                           q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2, sinks);
+                           q_blocks, page_size, shift, max_blocks, page_stride, kv_stride, window, scale2, sinks, cap_in);
     }
     if (e != cudaSuccess) { cudaGetLastError(); return zi_fail("decode_attention: launch failed: %s", cudaGetErrorString(e)); }
     return zi_check_launch("decode_attention");
@@ -909,7 +929,7 @@ static int dt_max_clusters() {
 struct DtArgs {
     const CUtensorMap* mkv; const void* q; void* out; const int* tables; const int* tok_seg; const int* pos; int* status;
     int n_tokens, n_heads, n_kv_heads, q_blocks, page_size, box_rows, max_blocks, window; float scale2; cudaStream_t stream;
-    int n_splits, min_split_tiles; float* part; int kv_box; const float* sinks; int one_plane;
+    int n_splits, min_split_tiles; float* part; int kv_box; const float* sinks; int one_plane; float cap_in;
 };
 
 template <int HD, int KEYS, int CL>
@@ -931,7 +951,8 @@ static cudaError_t dt_launch(const DtArgs& a) {
     cfg.dynamicSmemBytes = dt_smem<HD, KEYS>(); cfg.stream = a.stream;
     return cudaLaunchKernelEx(&cfg, decode_attention_tma_kernel<HD, KEYS, CL>, *a.mkv, (const bf16*)a.q, (bf16*)a.out, a.tables,
                               a.tok_seg, a.pos, a.status, a.n_heads, a.n_kv_heads, a.q_blocks, a.page_size, a.box_rows,
-                              a.max_blocks, a.window, a.scale2, a.n_splits, a.min_split_tiles, a.part, a.kv_box, a.sinks, a.one_plane);
+                              a.max_blocks, a.window, a.scale2, a.n_splits, a.min_split_tiles, a.part, a.kv_box, a.sinks, a.one_plane,
+                              a.cap_in);
 }
 template <int HD>
 static cudaError_t dt_dispatch(const DtArgs& a, int keys, int cl) {
@@ -1001,7 +1022,7 @@ ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* ou
                                       const int* pos, int* status, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                       int page_size, int max_blocks, long long n_pages, long long page_stride,
                                       long long kv_stride, int window, float scale, int max_kv_len, float* part,
-                                      long long part_floats, const float* sinks, cudaStream_t stream) {
+                                      long long part_floats, const float* sinks, float softcap, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (check_common("decode_attention_tma", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
     if (page_size < 8 || page_size > 128 || (page_size & (page_size - 1))) return zi_fail("decode_attention_tma: page size %d is not a power of two from 8 to 128", page_size);
@@ -1025,7 +1046,8 @@ ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* ou
     CUtensorMap mkv;
     if (tc_map_kv_pages(&mkv, cache, head_dim, page_size, n_kv_heads, n_pages, page_stride, kv_stride, box_rows, kv_box ? 2 : 1)) return 1;
     DtArgs a = {&mkv, q, out, tables, tok_seg, pos, status, n_tokens, n_heads, n_kv_heads, q_blocks, page_size, box_rows,
-                max_blocks, window, scale * LOG2E, stream, plan.splits, plan.min_split_tiles, part, kv_box, sinks, one_plane};
+                max_blocks, window, (softcap > 0.0f ? softcap : scale) * LOG2E, stream, plan.splits, plan.min_split_tiles, part, kv_box,
+                sinks, one_plane, softcap > 0.0f ? scale / softcap : 0.0f};
     cudaError_t e = head_dim == 128 ? dt_dispatch<128>(a, keys, plan.cl) : dt_dispatch<64>(a, keys, plan.cl);
     if (e != cudaSuccess) { cudaGetLastError(); return zi_fail("decode_attention_tma: launch failed: %s", cudaGetErrorString(e)); }
     if (plan.splits > 1) {
@@ -1039,25 +1061,25 @@ ZI_EXPORT int zi_decode_attention_tma(const void* q, const void* cache, void* ou
 ZI_EXPORT int zi_prefill_attention(const void* q, const void* cache, void* out, const int* tables, const int* tiles,
                                    const int* pos, int n_tiles, int n_heads, int n_kv_heads, int head_dim,
                                    int page_size, int max_blocks, long long page_stride, long long kv_stride,
-                                   int window, float scale, const float* sinks, cudaStream_t stream) {
+                                   int window, float scale, const float* sinks, float softcap, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (check_common("prefill_attention", n_heads, n_kv_heads, head_dim, page_size, max_blocks)) return 1;
     if (n_heads > 65535) return zi_fail("prefill_attention: %d heads are more than one launch takes", n_heads);
     dim3 grid(2 * n_tiles, n_heads);          // two 64-row halves per tile of the list
-    const float scale2 = scale * LOG2E;
+    const float scale2 = (softcap > 0.0f ? softcap : scale) * LOG2E, cap_in = softcap > 0.0f ? scale / softcap : 0.0f;
     const int shift = page_shift_of(page_size);
     if (head_dim == 128) {
         const size_t smem = 5 * TILE_KEYS * 128 * 2;
         if (set_smem(prefill_attention_kernel<128>, smem, "prefill_attention")) return 1;
         prefill_attention_kernel<128><<<grid, ATT_THREADS, smem, stream>>>(
             (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tiles, pos, n_heads, n_kv_heads, page_size, shift,
-            max_blocks, page_stride, kv_stride, window, scale2, sinks);
+            max_blocks, page_stride, kv_stride, window, scale2, sinks, cap_in);
     } else {
         const size_t smem = 5 * TILE_KEYS * 64 * 2;
         if (set_smem(prefill_attention_kernel<64>, smem, "prefill_attention")) return 1;
         prefill_attention_kernel<64><<<grid, ATT_THREADS, smem, stream>>>(
             (const bf16*)q, (const bf16*)cache, (bf16*)out, tables, tiles, pos, n_heads, n_kv_heads, page_size, shift,
-            max_blocks, page_stride, kv_stride, window, scale2, sinks);
+            max_blocks, page_stride, kv_stride, window, scale2, sinks, cap_in);
     }
     return zi_check_launch("prefill_attention");
 }

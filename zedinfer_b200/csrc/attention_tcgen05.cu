@@ -104,7 +104,9 @@ struct FaParams {
     const int* pos;
     int* status;
     int n_heads, n_kv_heads, page_size, max_blocks, window;
-    float scale2;                  // softmax scale x log2(e)
+    float scale2;                  // softmax scale x log2(e); with a score cap c: c x log2(e)
+    float cap_in;                  // 0: no cap; else scale / c: a raw score s becomes tanh(s cap_in) before the softmax, so that
+                                   // scale2 tanh(s cap_in) = log2(e) c tanh(s scale / c)
     const float* sinks;            // optional, one float per query head: exp(sinks[h]) joins the softmax's denominator
     int one_plane;                 // the cache has one plane, whose rows are keys and values at once
 };
@@ -309,6 +311,15 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_kv, con
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(s_empty + 8 * st) : "memory");
+            if (p.cap_in > 0.0f) {        // tanh(y) = 1 - 2 / (1 + exp(2 y)): one ex2 and one reciprocal, right at both ends
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const float y = __uint_as_float(s[q4][c]) * p.cap_in;
+                        s[q4][c] = __float_as_uint(1.0f - __fdividef(2.0f, 1.0f + fa_exp2(y * 2.8853900817779268f)));
+                    }
+            }
             // keys this row must not see; whole tiles below the diagonal and inside the window need no test
             const bool need_mask = key0 + FA_KEYS - 1 > p0 || (p.window > 0 && key0 < p_last - p.window + 1);
             if (need_mask) {
@@ -437,7 +448,7 @@ ZI_EXPORT int zi_prefill_attention_tcgen05(const void* q, const void* cache, voi
                                            const int* pos, int* status, int n_tokens, int n_tiles, int n_heads, int n_kv_heads,
                                            int head_dim, int page_size, int max_blocks, long long n_pages, long long page_stride,
                                            long long kv_stride, int window, float scale, const float* sinks,
-                                           cudaStream_t stream) {
+                                           float softcap, cudaStream_t stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return 0;
     if (head_dim != 64 && head_dim != 128) return zi_fail("prefill_attention_tcgen05: head_dim %d is not 64 or 128", head_dim);
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return zi_fail("prefill_attention_tcgen05: %d heads over %d key-value heads", n_heads, n_kv_heads);
@@ -452,7 +463,8 @@ ZI_EXPORT int zi_prefill_attention_tcgen05(const void* q, const void* cache, voi
     FaParams p;
     p.q = (const bf16*)q; p.out = (bf16*)out; p.tables = tables; p.tiles = tiles; p.pos = pos; p.status = status;
     p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.page_size = page_size; p.max_blocks = max_blocks; p.window = window;
-    p.scale2 = scale * 1.4426950408889634f;
+    p.scale2 = (softcap > 0.0f ? softcap : scale) * 1.4426950408889634f;
+    p.cap_in = softcap > 0.0f ? scale / softcap : 0.0f;
     p.sinks = sinks; p.one_plane = kv_stride == 0 ? 1 : 0;
     const dim3 grid(n_heads, n_tiles);
     const size_t smem = (size_t)FA_STAGE_OFFSET(head_dim) + (size_t)FA_ROWS * head_dim * 2;

@@ -598,10 +598,10 @@ def _check_sinks(sinks: Optional[torch.Tensor], n_heads: int) -> None:
 def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                      tok_seg: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                      page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
-                     sinks: Optional[torch.Tensor] = None) -> None:
+                     sinks: Optional[torch.Tensor] = None, softcap: Optional[float] = None) -> None:
     """One query token per request, bfloat16, tensor cores; a cluster of eight thread blocks per
     (request, key/value head) shares the context and merges through distributed shared memory.  ``kv_stride`` 0 and
-    ``sinks``: as :func:`paged_attention`."""
+    ``sinks`` and ``softcap``: as :func:`paged_attention`."""
     need_cuda(q, cache, out, tables, tok_seg, pos, sinks)
     _check_sinks(sinks, n_heads)
     need_int32("tables", tables), need_int32("tok_seg", tok_seg), need_int32("pos", pos)
@@ -612,7 +612,7 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, ta
     _attention_mma.call("zi_decode_attention", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tok_seg), ptr(pos),
                         c_int(n), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
                         c_int(tables.shape[1]), c_ll(page_stride), c_ll(kv_stride), c_int(window or 0),
-                        c_float(scale), ptr(sinks), stream())
+                        c_float(scale), ptr(sinks), c_float(softcap or 0.0), stream())
 
 
 def decode_attention_split_from() -> int:
@@ -624,7 +624,7 @@ def decode_attention_split_from() -> int:
 def decode_attention_tma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                          tok_seg: Optional[torch.Tensor], pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                          page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
-                         max_kv_len: int = 0, sinks: Optional[torch.Tensor] = None) -> None:
+                         max_kv_len: int = 0, sinks: Optional[torch.Tensor] = None, softcap: Optional[float] = None) -> None:
     """One query token per request, bfloat16: the cluster kernel with 32-key tiles dealt to single warps, each
     fed by TMA through the block table into a ring of its own.  Same arguments as :func:`decode_attention`;
     head_dim 64 or 128, pages of a power of two from 8 to 128 tokens.  ``max_kv_len``: an upper bound of the cached
@@ -652,14 +652,14 @@ def decode_attention_tma(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
                         ptr(_tc_status(q.device)), c_int(q.shape[0]), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
                         c_int(page_size), c_int(tables.shape[1]), c_ll(cache.shape[0]), c_ll(page_stride), c_ll(kv_stride),
                         c_int(window or 0), c_float(scale), c_int(int(max_kv_len) if part_floats else 0), ptr(part),
-                        c_ll(part_floats), ptr(sinks), stream())
+                        c_ll(part_floats), ptr(sinks), c_float(softcap or 0.0), stream())
     _tc_launched[q.device] = True
 
 
 def prefill_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                       tiles: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                       page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
-                      sinks: Optional[torch.Tensor] = None) -> None:
+                      sinks: Optional[torch.Tensor] = None, softcap: Optional[float] = None) -> None:
     """Portions of prompts, bfloat16, ``mma.sync`` tensor-core path.  ``tiles`` int32 ``[n_tiles, 3]``: (first token,
     rows <= 128, segment); the positions of a tile's tokens are consecutive.  Takes any page size and windows."""
     need_cuda(q, cache, out, tables, tiles, pos)
@@ -670,13 +670,13 @@ def prefill_attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, t
     _attention_mma.call("zi_prefill_attention", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tiles), ptr(pos),
                         c_int(tiles.shape[0]), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(page_size),
                         c_int(tables.shape[1]), c_ll(page_stride), c_ll(kv_stride), c_int(window or 0),
-                        c_float(scale), ptr(sinks), stream())
+                        c_float(scale), ptr(sinks), c_float(softcap or 0.0), stream())
 
 
 def prefill_attention_tcgen05(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, tables: torch.Tensor,
                               tiles: torch.Tensor, pos: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                               page_size: int, page_stride: int, kv_stride: int, window: Optional[int], scale: float,
-                              sinks: Optional[torch.Tensor] = None) -> None:
+                              sinks: Optional[torch.Tensor] = None, softcap: Optional[float] = None) -> None:
     """Portions of prompts, bfloat16, on tcgen05: scores and outputs accumulate in TMEM, K and V pages arrive by
     TMA through the block table.  Same arguments as :func:`prefill_attention`; head_dim 64 or 128, pages of a power
     of two from 8 to 128 tokens.  A bounded wait that runs out is reported by :func:`tcgen05_status`."""
@@ -688,7 +688,8 @@ def prefill_attention_tcgen05(q: torch.Tensor, cache: torch.Tensor, out: torch.T
     _attention_tcgen05.call("zi_prefill_attention_tcgen05", ptr(q), ptr(cache), ptr(out), ptr(tables), ptr(tiles), ptr(pos),
                             ptr(_tc_status(q.device)), c_int(q.shape[0]), c_int(tiles.shape[0]), c_int(n_heads),
                             c_int(n_kv_heads), c_int(head_dim), c_int(page_size), c_int(tables.shape[1]),
-                            c_ll(cache.shape[0]), c_ll(page_stride), c_ll(kv_stride), c_int(window or 0), c_float(scale), ptr(sinks), stream())
+                            c_ll(cache.shape[0]), c_ll(page_stride), c_ll(kv_stride), c_int(window or 0), c_float(scale), ptr(sinks),
+                            c_float(softcap or 0.0), stream())
     _tc_launched[q.device] = True
 
 
@@ -708,22 +709,22 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
     bfloat16 with head_dim 64 or 128 runs on the tensor cores: decode-only steps, and the single tokens at the head
     of a mixed step, on the cluster decode kernel, anything else on the tcgen05 prefill kernel (pages of 8..128 tokens) or the ``mma.sync`` prefill kernel (other
     page sizes); float32 and other head sizes on the general kernel.  ``sinks`` (float32, one per query head) and a cache
-    with one plane (``cache.kv_stride`` 0, rows that are keys and values at once) are taken by every kernel.  ``softcap``
-    (scores through ``c tanh(s / c)``): the general kernel.
+    with one plane (``cache.kv_stride`` 0, rows that are keys and values at once) are taken by every kernel, and so is
+    ``softcap`` (scores through ``c tanh(s / c)``).
     """
     tables = ctx.tables[cache.group]
-    if (q.dtype == torch.bfloat16 and head_dim in (64, 128) and softcap is None
+    if (q.dtype == torch.bfloat16 and head_dim in (64, 128)
             and (LATENT_TENSOR_CORES or (sinks is None and cache.kv_stride != 0))):
         n = q.shape[0]
         if ctx.decode_only and tcgen05_attention_ok(head_dim, cache.page_size):
             # in a step of single tokens, token n is segment n
             decode_attention_tma(q, cache.tensor, out, tables, None, ctx.positions, n_heads, n_kv_heads, head_dim,
                                  cache.page_size, cache.page_stride, cache.kv_stride, window, scale,
-                                 max_kv_len=min(ctx.max_kv_len, window) if window else ctx.max_kv_len, sinks=sinks)
+                                 max_kv_len=min(ctx.max_kv_len, window) if window else ctx.max_kv_len, sinks=sinks, softcap=softcap)
             return
         if ctx.decode_only:
             decode_attention(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads, head_dim,
-                             cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks)
+                             cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks, softcap=softcap)
             return
         tiles = ctx.extras.get("attn_tiles")
         lead = ctx.extras.get("leading_singles", 0) if tiles is not None else 0
@@ -731,18 +732,18 @@ def attention(q: torch.Tensor, cache, out: torch.Tensor, ctx, n_heads: int, n_kv
             if tcgen05_attention_ok(head_dim, cache.page_size):     # the leading single tokens are segments 0 .. lead - 1
                 decode_attention_tma(q[:lead], cache.tensor, out[:lead], tables, None, ctx.positions[:lead], n_heads,
                                      n_kv_heads, head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale,
-                                     sinks=sinks)
+                                     sinks=sinks, softcap=softcap)
             else:
                 decode_attention(q[:lead], cache.tensor, out[:lead], tables, ctx.tok_seg[:lead], ctx.positions[:lead], n_heads,
                                  n_kv_heads, head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale,
-                                 sinks=sinks)
+                                 sinks=sinks, softcap=softcap)
         if tiles is not None and tcgen05_attention_ok(head_dim, cache.page_size):
             prefill_attention_tcgen05(q, cache.tensor, out, tables, tiles, ctx.positions, n_heads, n_kv_heads, head_dim,
-                                      cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks)
+                                      cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks, softcap=softcap)
             return
         if tiles is not None:
             prefill_attention(q, cache.tensor, out, tables, tiles, ctx.positions, n_heads, n_kv_heads, head_dim,
-                              cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks)
+                              cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks, softcap=softcap)
             return
     paged_attention(q, cache.tensor, out, tables, ctx.tok_seg, ctx.positions, n_heads, n_kv_heads,
                     head_dim, cache.page_size, cache.page_stride, cache.kv_stride, window, scale, sinks=sinks, softcap=softcap)
