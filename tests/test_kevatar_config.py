@@ -167,7 +167,7 @@ def test_plain_mechanisms_agree_with_each_other():
     f, mag = KP.stretched_frequencies(sc, F64)
     f0, _ = KP.stretched_frequencies({"base": 10000.0, "dims": 32, "scaling": None}, F64)
     assert abs(mag - (0.1 * math.log(4.0) + 1.0)) < 1e-15
-    assert torch.equal(f[:4], f0[:4]) and torch.allclose(f[-3:], f0[-3:] / 4.0) and bool(((f <= f0) & (f >= f0 / 4.0 - 1e-18)).all())
+    assert torch.equal(f[:2], f0[:2]) and torch.allclose(f[-3:], f0[-3:] / 4.0) and bool(((f <= f0) & (f >= f0 / 4.0 - 1e-18)).all())
     assert 0 < int(((f < f0) & (f > f0 / 4.0 + 1e-15)).sum())
     # the convolution's last column meets the current token, the first the oldest
     u = torch.randn(6, 3, generator=g, dtype=F64)

@@ -222,7 +222,7 @@ def build_kevatar_spec(cfg: KevatarConfig) -> ModelSpec:
                 "hidden_size": cfg.width, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"],
                 "v_head_dim": m["vdim"], "position": position, "qkv_bias": False, "scale": m["scale"], "softcap": m["softcap"],
                 "window": m["window"], "shared_kv": not own, "names": names,
-                "cache_window": (keep[i] if m["window"] is not None else "own") if own else "own"})
+                "cache_window": keep[i] if own else "own"})
         elif layer.type == "channel_delta":
             if m["decay_rank"] is None or m["gate_rank"] is None:
                 raise ConfigError(f"config.json: layers[{i}].mixer: 'decay_rank' and 'gate_rank' are neither named nor known "
