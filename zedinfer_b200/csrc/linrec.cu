@@ -39,9 +39,107 @@ __device__ __forceinline__ float lr_softplus(float x) { return x > 20.0f ? x : l
 __device__ __forceinline__ float lr_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float lr_silu(float x) { return x / (1.0f + expf(-x)); }
 
-// A thread holds R entries of one column: entries i * 32 + sub * 4 + e (i < R / 4, e < 4), sub = lane & 7, so that the
-// eight lanes of a column read 128 consecutive bytes of a staged vector at a time.  DP = 8 * R >= dim; what lies past
-// dim is zero.
+// ---- what both forms of the walk share, so that a token has the same bits whichever form walked it ------------------
+// One warp makes a token's query and key of one query/key head ready: SiLU where asked, unit vectors (times q_scale for the
+// query) in the delta rule, zero past dim; DP floats each to dq and dk (shared or global memory).  Returns q . k.
+template <typename T, int DP, bool DELTA>
+__device__ __forceinline__ float lr_ready_qk(const T* __restrict__ qr, const T* __restrict__ kr, int dim, int act_silu, float q_scale,
+                                             float unit_eps, int lane, float* dq, float* dk) {
+    float qv[DP / 32], kv[DP / 32];
+    float qq = 0.0f, kk = 0.0f;
+#pragma unroll
+    for (int j = 0; j < DP / 32; ++j) {
+        const int d = lane + 32 * j;
+        float x = d < dim ? to_f32<T>(qr[d]) : 0.0f, z = d < dim ? to_f32<T>(kr[d]) : 0.0f;
+        if (act_silu) { x = lr_silu(x); z = lr_silu(z); }
+        qv[j] = x; kv[j] = z;
+        qq = fmaf(x, x, qq); kk = fmaf(z, z, kk);
+    }
+    float qs = q_scale, ks = 1.0f;
+    if (DELTA) {
+        qq = warp_sum(qq); kk = warp_sum(kk);
+        qs = q_scale / sqrtf(qq + unit_eps);
+        ks = 1.0f / sqrtf(kk + unit_eps);
+    }
+    float dot = 0.0f;
+#pragma unroll
+    for (int j = 0; j < DP / 32; ++j) {
+        const int d = lane + 32 * j;
+        const float x = qv[j] * qs, z = kv[j] * ks;
+        dq[d] = x; dk[d] = z;
+        dot = fmaf(x, z, dot);
+    }
+    return warp_sum(dot);
+}
+
+// The decay of one head and key entry: exp(-rate softplus(a + dt_bias)).
+__device__ __forceinline__ float lr_decay(float a, float dt_bias, float rate) { return expf(-rate * lr_softplus(a + dt_bias)); }
+
+// One token through the R entries a thread holds of its column.  A thread holds entries i * 32 + sub * 4 + e (i < R / 4,
+// e < 4), sub = lane & 7, so that the eight lanes of a column read 128 consecutive bytes of a staged vector at a time.
+// LrTok: what a thread needs of a token, in registers, so that the next token's loads can be in flight while this one walks.
+template <int R, bool DELTA>
+struct LrTok {
+    float k[R], q[R], g[DELTA ? R : 1];
+    float v, beta, qk;
+};
+
+// sk, sq, sg: the token's staged key, query and decays (8 R floats each; what lies past dim is zero).
+template <int R, bool DELTA>
+__device__ __forceinline__ void lr_load_token(LrTok<R, DELTA>& t, const float* sk, const float* sq, const float* sg, float vv, float beta,
+                                              float qk, int sub) {
+#pragma unroll
+    for (int i = 0; i < R / 4; ++i) {
+        const int at = i * 32 + sub * 4;
+        const float4 k4 = *reinterpret_cast<const float4*>(sk + at);
+        const float4 q4 = *reinterpret_cast<const float4*>(sq + at);
+        t.k[i * 4] = k4.x; t.k[i * 4 + 1] = k4.y; t.k[i * 4 + 2] = k4.z; t.k[i * 4 + 3] = k4.w;
+        t.q[i * 4] = q4.x; t.q[i * 4 + 1] = q4.y; t.q[i * 4 + 2] = q4.z; t.q[i * 4 + 3] = q4.w;
+        if (DELTA) {
+            const float4 g4 = *reinterpret_cast<const float4*>(sg + at);
+            t.g[i * 4] = g4.x; t.g[i * 4 + 1] = g4.y; t.g[i * 4 + 2] = g4.z; t.g[i * 4 + 3] = g4.w;
+        }
+    }
+    t.v = vv; t.beta = beta; t.qk = qk;
+}
+
+// Returns the column's output on all eight lanes.  With S the state before the token:
+//   delta  u = beta (v - sum (k g) S);  o = sum (q g) S + (q . k) u;  S <- g S + k u
+//   decay  o = lambda sum q S + (q . k) v;                            S <- lambda S + k v
+// so that only the sum over k (delta) lies between one token's state and the next one's: the products with g and the sum
+// over q wait for nothing but S.
+template <int R, bool DELTA>
+__device__ __forceinline__ float lr_walk_token(float (&S)[R], const LrTok<R, DELTA>& t, float lam) {
+    float ks[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        if (DELTA) {
+            ks[i & 3] = fmaf(t.k[i] * t.g[i], S[i], ks[i & 3]);
+            qs[i & 3] = fmaf(t.q[i] * t.g[i], S[i], qs[i & 3]);
+        } else {
+            qs[i & 3] = fmaf(t.q[i], S[i], qs[i & 3]);
+        }
+    }
+    float kss = (ks[0] + ks[1]) + (ks[2] + ks[3]), qss = (qs[0] + qs[1]) + (qs[2] + qs[3]);
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+        if (DELTA) kss += __shfl_xor_sync(0xffffffffu, kss, o);
+        qss += __shfl_xor_sync(0xffffffffu, qss, o);
+    }
+    if (DELTA) {
+        const float u = t.beta * (t.v - kss);
+#pragma unroll
+        for (int i = 0; i < R; ++i) S[i] = fmaf(t.k[i], u, t.g[i] * S[i]);
+        return fmaf(t.qk, u, qss);
+    } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i) S[i] = fmaf(t.k[i], t.v, lam * S[i]);
+        return fmaf(t.qk, t.v, lam * qss);
+    }
+}
+
+// ---- the walk that makes its own inputs ready (steps of single tokens) -----------------------------------------------------
+// DP = 8 * R >= dim; what lies past dim is zero.
 template <typename T, int R, bool DELTA>
 __global__ void __launch_bounds__(LR_THREADS)
 linear_state_kernel(const LinearStateArgs p, int tiles) {
@@ -82,41 +180,15 @@ linear_state_kernel(const LinearStateArgs p, int tiles) {
         // ---- stage: q, k (unit vectors in the delta rule), the decays, q . k; a warp per token
         for (int tt = warp; tt < cnt; tt += LR_THREADS / 32) {
             const size_t n = (size_t)(c0 + tt);
-            const T* qr = q + n * p.ldq + (size_t)kvh * dim;
-            const T* kr = k + n * p.ldk + (size_t)kvh * dim;
-            float qv[DP / 32], kv[DP / 32];
-            float qq = 0.0f, kk = 0.0f;
-#pragma unroll
-            for (int j = 0; j < DP / 32; ++j) {
-                const int d = lane + 32 * j;
-                float x = d < dim ? to_f32<T>(qr[d]) : 0.0f, z = d < dim ? to_f32<T>(kr[d]) : 0.0f;
-                if (p.act_silu) { x = lr_silu(x); z = lr_silu(z); }
-                qv[j] = x; kv[j] = z;
-                qq = fmaf(x, x, qq); kk = fmaf(z, z, kk);
-            }
-            float qs = p.q_scale, ks = 1.0f;
+            const float dot = lr_ready_qk<T, DP, DELTA>(q + n * p.ldq + (size_t)kvh * dim, k + n * p.ldk + (size_t)kvh * dim, dim,
+                                                        p.act_silu, p.q_scale, p.unit_eps, lane, sq + tt * DP, sk + tt * DP);
             if (DELTA) {
-                qq = warp_sum(qq); kk = warp_sum(kk);
-                qs = p.q_scale / sqrtf(qq + p.unit_eps);
-                ks = 1.0f / sqrtf(kk + p.unit_eps);
-            }
-            float dot = 0.0f;
 #pragma unroll
-            for (int j = 0; j < DP / 32; ++j) {
-                const int d = lane + 32 * j;
-                const float x = qv[j] * qs, z = kv[j] * ks;
-                sq[tt * DP + d] = x; sk[tt * DP + d] = z;
-                dot = fmaf(x, z, dot);
-                if (DELTA) {
-                    float g = 1.0f;
-                    if (d < dim) {
-                        const float pre = to_f32<T>(a[n * p.lda + (size_t)h * dim + d]) + p.dt_bias[(size_t)h * dim + d];
-                        g = expf(-rate * lr_softplus(pre));
-                    }
-                    sg[tt * DP + d] = g;
+                for (int j = 0; j < DP / 32; ++j) {
+                    const int d = lane + 32 * j;
+                    sg[tt * DP + d] = d < dim ? lr_decay(to_f32<T>(a[n * p.lda + (size_t)h * dim + d]), p.dt_bias[(size_t)h * dim + d], rate) : 0.0f;
                 }
             }
-            dot = warp_sum(dot);
             if (lane == 0) {
                 sqk[tt] = dot;
                 sbeta[tt] = DELTA ? lr_sigmoid(to_f32<T>(b[n * p.ldb + h])) : 1.0f;
@@ -131,35 +203,10 @@ linear_state_kernel(const LinearStateArgs p, int tiles) {
         __syncthreads();
         // ---- walk
         for (int tt = 0; tt < cnt; ++tt) {
-            float kr[R];
-            float kS = 0.0f, qS = 0.0f;
-#pragma unroll
-            for (int i = 0; i < R / 4; ++i) {
-                const int at = tt * DP + i * 32 + sub * 4;
-                const float4 k4 = *reinterpret_cast<const float4*>(sk + at);
-                const float4 q4 = *reinterpret_cast<const float4*>(sq + at);
-                float4 g4 = make_float4(lam, lam, lam, lam);
-                if (DELTA) g4 = *reinterpret_cast<const float4*>(sg + at);
-                const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w}, gg[4] = {g4.x, g4.y, g4.z, g4.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float s = S[i * 4 + e] * gg[e];
-                    S[i * 4 + e] = s;
-                    kr[i * 4 + e] = kk[e];
-                    if (DELTA) kS = fmaf(kk[e], s, kS);
-                    qS = fmaf(qq[e], s, qS);
-                }
-            }
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-                if (DELTA) kS += __shfl_xor_sync(0xffffffffu, kS, o);
-                qS += __shfl_xor_sync(0xffffffffu, qS, o);
-            }
-            const float vv = sv[tt * LR_COLS + (threadIdx.x >> 3)];
-            const float u = DELTA ? sbeta[tt] * (vv - kS) : vv;
-#pragma unroll
-            for (int i = 0; i < R; ++i) S[i] = fmaf(kr[i], u, S[i]);
-            if (sub == 0 && live) p.y[(size_t)(c0 + tt) * ((size_t)p.heads * vdim) + (size_t)h * vdim + col] = fmaf(sqk[tt], u, qS);
+            LrTok<R, DELTA> tok;
+            lr_load_token<R, DELTA>(tok, sk + tt * DP, sq + tt * DP, sg + tt * DP, sv[tt * LR_COLS + (threadIdx.x >> 3)], sbeta[tt], sqk[tt], sub);
+            const float o = lr_walk_token<R, DELTA>(S, tok, lam);
+            if (sub == 0 && live) p.y[(size_t)(c0 + tt) * ((size_t)p.heads * vdim) + (size_t)h * vdim + col] = o;
         }
     }
     if (srow) {
@@ -188,6 +235,189 @@ static int launch_linear_state(const LinearStateArgs& p, cudaStream_t stream) {
     return zi_check_launch("linear_state");
 }
 
+// ---- the walk over inputs made ready beforehand (steps that bring portions of prompts) ---------------------------------
+// Making a token ready (loads from global memory, unit vectors, softplus and exponentials) does not depend on the state, so
+// for long segments it runs first, over all tokens and heads at once, and leaves per token and head one record of float32
+//   [ q DP | k DP | g DP (delta) | beta, q . k, 0, 0 ]
+// and the values [tiles * LR_COLS] (SiLU applied where asked, zero past vdim).  The walk then only copies records into
+// shared memory, two chunks in flight, and walks.  Both forms call the same functions on a token, so its result has the
+// same bits in either.
+template <bool DELTA, int DP> struct LrRecord { static constexpr int SIZE = (DELTA ? 3 : 2) * DP + 4; };
+
+template <typename T, int R, bool DELTA>
+__global__ void __launch_bounds__(LR_THREADS)
+linear_state_ready_kernel(const LinearStateArgs p, float* __restrict__ rec, float* __restrict__ pv, int n_tokens, int vp) {
+    constexpr int DP = 8 * R, REC = LrRecord<DELTA, DP>::SIZE;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long pair = (long long)blockIdx.x * (LR_THREADS / 32) + warp;
+    if (pair >= (long long)n_tokens * p.heads) return;
+    const size_t n = (size_t)(pair / p.heads);
+    const int h = (int)(pair - (long long)n * p.heads), kvh = h / (p.heads / p.kv_heads);
+    const int dim = p.dim, vdim = p.vdim;
+    const T* q = (const T*)p.q; const T* k = (const T*)p.k; const T* v = (const T*)p.v;
+    float* r = rec + (size_t)pair * REC;
+    const float dot = lr_ready_qk<T, DP, DELTA>(q + n * p.ldq + (size_t)kvh * dim, k + n * p.ldk + (size_t)kvh * dim, dim, p.act_silu,
+                                                p.q_scale, p.unit_eps, lane, r, r + DP);
+    float beta = 1.0f;
+    if (DELTA) {
+        const T* a = (const T*)p.a;
+        const float rate = expf(p.a_log[h]);
+#pragma unroll
+        for (int j = 0; j < DP / 32; ++j) {
+            const int d = lane + 32 * j;
+            r[2 * DP + d] = d < dim ? lr_decay(to_f32<T>(a[n * p.lda + (size_t)h * dim + d]), p.dt_bias[(size_t)h * dim + d], rate) : 0.0f;
+        }
+        beta = lr_sigmoid(to_f32<T>(((const T*)p.b)[n * p.ldb + h]));
+    }
+    if (lane < 4) r[REC - 4 + lane] = lane == 0 ? beta : (lane == 1 ? dot : 0.0f);
+    float* vr = pv + (size_t)pair * vp;
+    for (int c = lane; c < vp; c += 32) {
+        float x = c < vdim ? to_f32<T>(v[n * p.ldv + (size_t)h * vdim + c]) : 0.0f;
+        if (p.act_silu) x = lr_silu(x);
+        vr[c] = x;
+    }
+}
+
+__device__ __forceinline__ void lr_copy16(float* dst, const float* src) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(src) : "memory");
+}
+
+template <int R, bool DELTA>
+__global__ void __launch_bounds__(LR_THREADS)
+linear_state_walk_kernel(const LinearStateArgs p, const float* __restrict__ rec, const float* __restrict__ pv, int tiles) {
+    constexpr int DP = 8 * R, REC = LrRecord<DELTA, DP>::SIZE;
+    constexpr int STAGE = LR_CHUNK * (REC + LR_COLS);                      // a chunk's records, then its values
+    constexpr bool PIPE = R <= 16;                                         // a second token's registers fit
+    extern __shared__ __align__(16) float smem[];
+    const int seg = blockIdx.x / tiles, tile = blockIdx.x - seg * tiles, h = blockIdx.y;
+    const int sub = threadIdx.x & 7;
+    const int col = tile * LR_COLS + (threadIdx.x >> 3);
+    const bool live = col < p.vdim;
+    const int t0 = p.bounds ? p.bounds[2 * seg] : seg, t1 = p.bounds ? p.bounds[2 * seg + 1] : seg + 1;
+    const int slot = p.slots[seg];
+    const int dim = p.dim, vdim = p.vdim, vp = tiles * LR_COLS;
+
+    float S[R];
+    float* srow = (slot >= 0 && live) ? p.state + (size_t)slot * p.slot_stride + ((size_t)h * vdim + col) * dim : nullptr;
+#pragma unroll
+    for (int i = 0; i < R / 4; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int d = i * 32 + sub * 4 + e;
+            S[i * 4 + e] = (srow && d < dim) ? srow[d] : 0.0f;
+        }
+    const float lam = DELTA ? 0.0f : p.decay[h];
+
+    auto fetch = [&](int c0, float* dst) {
+        const int cnt = min(LR_CHUNK, t1 - c0);
+        for (int idx = threadIdx.x; idx < cnt * (REC / 4); idx += LR_THREADS) {
+            const int tt = idx / (REC / 4), g = idx - tt * (REC / 4);
+            lr_copy16(dst + tt * REC + g * 4, rec + ((size_t)(c0 + tt) * p.heads + h) * REC + g * 4);
+        }
+        for (int idx = threadIdx.x; idx < cnt * (LR_COLS / 4); idx += LR_THREADS) {
+            const int tt = idx / (LR_COLS / 4), g = idx - tt * (LR_COLS / 4);
+            lr_copy16(dst + LR_CHUNK * REC + tt * LR_COLS + g * 4, pv + ((size_t)(c0 + tt) * p.heads + h) * vp + tile * LR_COLS + g * 4);
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+
+    if (t0 < t1) fetch(t0, smem);
+    int s = 0;
+    for (int c0 = t0; c0 < t1; c0 += LR_CHUNK, s ^= 1) {
+        const int cnt = min(LR_CHUNK, t1 - c0);
+        if (c0 + LR_CHUNK < t1) {
+            fetch(c0 + LR_CHUNK, smem + (s ^ 1) * STAGE);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();                                                   // everyone's copies of this chunk have landed
+        const float* st = smem + s * STAGE;
+        const float* sv = st + LR_CHUNK * REC + (threadIdx.x >> 3);
+        float* yc = p.y + (size_t)c0 * ((size_t)p.heads * vdim) + (size_t)h * vdim + col;
+        auto load = [&](LrTok<R, DELTA>& t, int tt) {
+            const float* r = st + tt * REC;
+            lr_load_token<R, DELTA>(t, r + DP, r, r + 2 * DP, sv[tt * LR_COLS], r[REC - 4], r[REC - 3], sub);
+        };
+        if (PIPE) {
+            // two tokens by turns: one's loads are in flight while the other walks
+            LrTok<R, DELTA> ta, tb;
+            load(ta, 0);
+            for (int tt = 0; tt < cnt; tt += 2) {
+                const bool second = tt + 1 < cnt;
+                if (second) load(tb, tt + 1);
+                const float oa = lr_walk_token<R, DELTA>(S, ta, lam);
+                if (sub == 0 && live) yc[(size_t)tt * ((size_t)p.heads * vdim)] = oa;
+                if (second) {
+                    if (tt + 2 < cnt) load(ta, tt + 2);
+                    const float ob = lr_walk_token<R, DELTA>(S, tb, lam);
+                    if (sub == 0 && live) yc[(size_t)(tt + 1) * ((size_t)p.heads * vdim)] = ob;
+                }
+            }
+        } else {
+            for (int tt = 0; tt < cnt; ++tt) {
+                LrTok<R, DELTA> tok;
+                load(tok, tt);
+                const float o = lr_walk_token<R, DELTA>(S, tok, lam);
+                if (sub == 0 && live) yc[(size_t)tt * ((size_t)p.heads * vdim)] = o;
+            }
+        }
+        __syncthreads();                                                   // this chunk's buffer may be filled again
+    }
+    if (srow) {
+#pragma unroll
+        for (int i = 0; i < R / 4; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int d = i * 32 + sub * 4 + e;
+                if (d < dim) srow[d] = S[i * 4 + e];
+            }
+    }
+}
+
+template <typename T, int R, bool DELTA>
+static int launch_linear_state_ready(const LinearStateArgs& p, float* work, int n_tokens, cudaStream_t stream) {
+    constexpr int REC = LrRecord<DELTA, 8 * R>::SIZE;
+    const int tiles = (p.vdim + LR_COLS - 1) / LR_COLS, vp = tiles * LR_COLS;
+    const long long pairs = (long long)n_tokens * p.heads;
+    float* rec = work;
+    float* pv = work + (size_t)pairs * REC;
+    const long long blocks = (pairs + LR_THREADS / 32 - 1) / (LR_THREADS / 32);
+    if (blocks > 2147483647LL) return zi_fail("linear_state: %lld tokens x heads are too many for one step", pairs);
+    linear_state_ready_kernel<T, R, DELTA><<<(unsigned)blocks, LR_THREADS, 0, stream>>>(p, rec, pv, n_tokens, vp);
+    if (int rc = zi_check_launch("linear_state_ready")) return rc;
+    const size_t smem = (size_t)2 * LR_CHUNK * (REC + LR_COLS) * sizeof(float);
+    if (smem > 48 * 1024) {
+        static bool raised = false;       // per instantiation
+        if (!raised) {
+            cudaFuncSetAttribute(linear_state_walk_kernel<R, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            raised = true;
+        }
+    }
+    linear_state_walk_kernel<R, DELTA><<<dim3((unsigned)(p.n_segments * tiles), (unsigned)p.heads), LR_THREADS, smem, stream>>>(p, rec, pv, tiles);
+    return zi_check_launch("linear_state_walk");
+}
+
+// floats of workspace the form with inputs made ready needs for a step
+static long long linear_state_work_floats(int rule, int n_tokens, int heads, int dim, int vdim) {
+    const int dp = dim <= 32 ? 32 : dim <= 64 ? 64 : dim <= 128 ? 128 : 256;
+    const int rec = (rule == 0 ? 3 : 2) * dp + 4, vp = (vdim + LR_COLS - 1) / LR_COLS * LR_COLS;
+    return (long long)n_tokens * heads * (rec + vp);
+}
+
+ZI_EXPORT long long zi_linear_state_work_floats(int rule, int n_tokens, int heads, int dim, int vdim) {
+    return linear_state_work_floats(rule, n_tokens, heads, dim, vdim);
+}
+
+template <typename T, bool DELTA>
+static int pick_linear_state_ready(const LinearStateArgs& p, float* work, int n_tokens, cudaStream_t stream) {
+    if (p.dim <= 32) return launch_linear_state_ready<T, 4, DELTA>(p, work, n_tokens, stream);
+    if (p.dim <= 64) return launch_linear_state_ready<T, 8, DELTA>(p, work, n_tokens, stream);
+    if (p.dim <= 128) return launch_linear_state_ready<T, 16, DELTA>(p, work, n_tokens, stream);
+    return launch_linear_state_ready<T, 32, DELTA>(p, work, n_tokens, stream);
+}
+
 template <typename T, bool DELTA>
 static int pick_linear_state(const LinearStateArgs& p, cudaStream_t stream) {
     if (p.dim <= 32) return launch_linear_state<T, 4, DELTA>(p, stream);
@@ -200,7 +430,7 @@ ZI_EXPORT int zi_linear_state(int rule, const void* q, long long ldq, const void
                               const void* a, long long lda, const void* b, long long ldb, int dtype, const float* dt_bias,
                               const float* a_log, const float* decay, float* state, long long slot_stride, const int* slots,
                               const int* bounds, float* y, int n_tokens, int n_segments, int heads, int kv_heads, int dim, int vdim,
-                              int act_silu, float q_scale, float unit_eps, cudaStream_t stream) {
+                              int act_silu, float q_scale, float unit_eps, float* work, long long work_floats, cudaStream_t stream) {
     if (n_tokens <= 0 || n_segments <= 0) return 0;
     if (rule != 0 && rule != 1) return zi_fail("linear_state: rule %d is neither 0 (delta) nor 1 (decay)", rule);
     if (heads <= 0 || kv_heads <= 0 || heads % kv_heads) return zi_fail("linear_state: %d heads cannot share %d query/key heads", heads, kv_heads);
@@ -216,6 +446,17 @@ ZI_EXPORT int zi_linear_state(int rule, const void* q, long long ldq, const void
     p.state = state; p.slot_stride = slot_stride; p.slots = slots; p.bounds = bounds; p.y = y;
     p.n_segments = n_segments; p.heads = heads; p.kv_heads = kv_heads; p.dim = dim; p.vdim = vdim; p.act_silu = act_silu;
     p.q_scale = q_scale; p.unit_eps = unit_eps;
+    if (work) {
+        // inputs made ready first, then the walk
+        if (((size_t)work & 15) != 0) return zi_fail("linear_state: the workspace must start on a 16-byte boundary");
+        if (work_floats < linear_state_work_floats(rule, n_tokens, heads, dim, vdim))
+            return zi_fail("linear_state: a workspace of %lld floats is too small for %d tokens", work_floats, n_tokens);
+        ZI_DISPATCH(dtype, T, {
+            if (rule == 0) return pick_linear_state_ready<T, true>(p, work, n_tokens, stream);
+            return pick_linear_state_ready<T, false>(p, work, n_tokens, stream);
+        });
+        return 0;
+    }
     ZI_DISPATCH(dtype, T, {
         if (rule == 0) return pick_linear_state<T, true>(p, stream);
         return pick_linear_state<T, false>(p, stream);

@@ -38,7 +38,7 @@ __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", 
            "moe_group", "moe_gemm", "moe_combine", "linear_gated_clamp_mul", "linear_relu2", "moe_group_padded",
            "moe_gather_rows", "gemm_tcgen05_grouped", "route", "rotary", "latent_prepare", "sigmoid_mul", "segment_bounds",
            "causal_conv_silu", "conv_state_update", "ssm_scan", "gated_group_rmsnorm", "rotary_norm", "norm_add", "gelu_mul_rows",
-           "linear_state", "group_rmsnorm_gate"]
+           "linear_state", "linear_state_work_floats", "group_rmsnorm_gate"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
@@ -1329,7 +1329,7 @@ def linear_state(rule: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
                  bounds: Optional[torch.Tensor], y: torch.Tensor, n_segments: int, heads: int, kv_heads: int, dim: int, vdim: int,
                  a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None,
                  a_log: Optional[torch.Tensor] = None, decay: Optional[torch.Tensor] = None, act_silu: bool = False,
-                 q_scale: float = 1.0, unit_eps: float = 1e-6) -> None:
+                 q_scale: float = 1.0, unit_eps: float = 1e-6, work: Optional[torch.Tensor] = None) -> None:
     """Walk each segment's tokens in order through a float32 state ``S`` (``dim x vdim``) per head.
 
     ``rule="delta"``: ``S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` with ``q`` and ``k`` made unit vectors
@@ -1340,8 +1340,14 @@ def linear_state(rule: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
     query/key head ``h // (heads / kv_heads)``) and ``v [tokens, heads * vdim]`` may have strided rows; ``y`` float32
     ``[tokens, heads * vdim]``.  A request's state (``[heads, vdim, dim]``, the first entries of its slot of ``state``) is read
     at the start and written back at the end; slot -1: zero, not written.  ``bounds`` from :func:`segment_bounds`; None:
-    segment s is token s."""
-    need_cuda(q, k, v, state, slots, bounds, y, a, b, dt_bias, a_log, decay)
+    segment s is token s.
+
+    ``work`` (float32, at least :func:`linear_state_work_floats` entries): a first kernel makes every token's inputs ready
+    there (all tokens and heads at once) and the walk only copies and walks, which pays for segments of many tokens; without
+    it the walk makes its inputs ready itself.  A token's result has the same bits either way."""
+    need_cuda(q, k, v, state, slots, bounds, y, a, b, dt_bias, a_log, decay, work)
+    if work is not None and (work.dtype != torch.float32 or not work.is_contiguous()):
+        raise KernelError("linear_state: the workspace must be contiguous float32")
     need_int32("slots", slots)
     need_contiguous("y", y)
     n = q.shape[0]
@@ -1362,7 +1368,16 @@ def linear_state(rule: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
                  c_ll(v.stride(0)), ptr(a), c_ll(a.stride(0) if a is not None else 0), ptr(b), c_ll(b.stride(0) if b is not None else 0),
                  c_int(dtype_code(q.dtype)), ptr(dt_bias), ptr(a_log), ptr(decay), sp, ss, ptr(slots), ptr(bounds), ptr(y), c_int(n),
                  c_int(n_segments), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(1 if act_silu else 0),
-                 c_float(q_scale), c_float(unit_eps), stream())
+                 c_float(q_scale), c_float(unit_eps), ptr(work), c_ll(work.numel() if work is not None else 0), stream())
+
+
+def linear_state_work_floats(rule: str, n_tokens: int, heads: int, dim: int, vdim: int) -> int:
+    """Entries of the float32 workspace :func:`linear_state` needs to make ``n_tokens`` tokens ready beforehand: per token
+    and head a record of q, k (and the decays in the delta rule) padded to the kernel's 32, 64, 128 or 256 entries plus
+    four scalars, and the values padded to whole tiles of 16 columns."""
+    padded = 32 if dim <= 32 else 64 if dim <= 64 else 128 if dim <= 128 else 256
+    record = (3 if LINEAR_STATE_RULES[rule] == 0 else 2) * padded + 4
+    return n_tokens * heads * (record + (vdim + 15) // 16 * 16)
 
 
 def group_rmsnorm_gate(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, n_groups: int, eps: float, out: torch.Tensor) -> None:

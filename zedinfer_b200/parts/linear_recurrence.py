@@ -50,6 +50,14 @@ def _stack_padded(tensors: Sequence[torch.Tensor], multiple: int = 8):
     return torch.cat(rows, dim=0).contiguous(), offsets
 
 
+def _walk_workspace(rule: str, ctx: StepContext, n: int, heads: int, dim: int, vdim: int) -> Optional[torch.Tensor]:
+    """The float32 workspace in which a step that brings portions of prompts makes its tokens ready before the walk; a step
+    of single tokens needs none (its walk makes them ready itself, in one launch)."""
+    if ctx.decode_only or n <= ctx.n_segments:
+        return None
+    return ctx.empty(ops.linear_state_work_floats(rule, n, heads, dim, vdim), dtype=torch.float32)
+
+
 def _state_and_slots(cache: CallCacheView, ctx: StepContext, owns_cache: bool, what: str) -> torch.Tensor:
     if cache.kind != "state" or not owns_cache:
         raise RuntimeError(f"{what} needs a state slot of its own")
@@ -133,7 +141,7 @@ class ChannelDeltaMixer(Mixer):
         ops.linear_state("delta", qkv[:, :self.qk_width], qkv[:, self.qk_width:2 * self.qk_width], qkv[:, 2 * self.qk_width:], state,
                          ctx.slots, bounds, y, ctx.n_segments, self.heads, self.kv_heads, self.dim, self.vdim, a=a,
                          b=proj[:, o_b:o_b + self.heads], dt_bias=self.dt_bias, a_log=self.a_log, q_scale=self.dim ** -0.5,
-                         unit_eps=UNIT_EPS)
+                         unit_eps=UNIT_EPS, work=_walk_workspace("delta", ctx, n, self.heads, self.dim, self.vdim))
         normed = ctx.empty(n, self.inner)
         ops.group_rmsnorm_gate(y, gate, self.g, self.heads, self.eps, normed)
         out = ctx.empty(n, self.hidden_size)
@@ -186,7 +194,7 @@ class LightningMixer(Mixer):
         y = ctx.empty(n, self.inner, dtype=torch.float32)
         ops.linear_state("decay", proj[:, o_q:o_q + self.qk_width], proj[:, o_k:o_k + self.qk_width], proj[:, o_v:o_v + self.inner],
                          state, ctx.slots, step_segment_bounds(ctx), y, ctx.n_segments, self.heads, self.heads, self.dim, self.vdim,
-                         decay=self.decay, act_silu=True)
+                         decay=self.decay, act_silu=True, work=_walk_workspace("decay", ctx, n, self.heads, self.dim, self.vdim))
         normed = ctx.empty(n, self.inner)
         ops.group_rmsnorm_gate(y, proj[:, o_g:o_g + self.inner], self.g, 1, self.eps, normed)
         out = ctx.empty(n, self.hidden_size)
