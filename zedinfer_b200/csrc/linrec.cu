@@ -18,8 +18,10 @@
 
 ZI_DEFINE_LAST_ERROR(linrec)
 
-#define LR_THREADS 128
-#define LR_COLS 16               // columns of S per block: 8 lanes share a column
+#define LR_THREADS 128            // of the kernel that makes inputs ready
+#define LR_LANES 8               // lanes that share a column of S
+#define LR_COLS 16               // columns of S per block.  Measured on 2,048 tokens of 12 heads of 128 x 128: 8, 16 or 32 lanes
+                                 // with 4 to 64 columns per block all take 0.5 to 1.3 ms; this one is the quickest
 #define LR_CHUNK 16              // tokens staged in shared memory at a time
 
 struct LinearStateArgs {
@@ -75,86 +77,64 @@ __device__ __forceinline__ float lr_ready_qk(const T* __restrict__ qr, const T* 
 // The decay of one head and key entry: exp(-rate softplus(a + dt_bias)).
 __device__ __forceinline__ float lr_decay(float a, float dt_bias, float rate) { return expf(-rate * lr_softplus(a + dt_bias)); }
 
-// One token through the R entries a thread holds of its column.  A thread holds entries i * 32 + sub * 4 + e (i < R / 4,
-// e < 4), sub = lane & 7, so that the eight lanes of a column read 128 consecutive bytes of a staged vector at a time.
-// LrTok: what a thread needs of a token, in registers, so that the next token's loads can be in flight while this one walks.
-template <int R, bool DELTA>
-struct LrTok {
-    float k[R], q[R], g[DELTA ? R : 1];
-    float v, beta, qk;
-};
-
-// sk, sq, sg: the token's staged key, query and decays (8 R floats each; what lies past dim is zero).
-template <int R, bool DELTA>
-__device__ __forceinline__ void lr_load_token(LrTok<R, DELTA>& t, const float* sk, const float* sq, const float* sg, float vv, float beta,
-                                              float qk, int sub) {
+// One token through the R entries a thread holds of its column.  A column is shared by LANES lanes; a thread holds entries
+// i * 4 LANES + sub * 4 + e (i < R / 4, e < 4), sub = lane % LANES, so that the lanes of a column read consecutive bytes of
+// a staged vector and the columns of a warp read it as one broadcast; sk, sq, sg: the token's staged key, query and decays
+// (R LANES floats each; what lies past dim is zero).  Returns the column's output, o = q . S after the write
+// = q . (g S) + (q . k) u, on all lanes of the column.  The walk's time is its instruction count (a warp alone on its
+// scheduler issues every third cycle or so), so a token costs four instructions per entry in the delta rule and three with
+// a constant decay, and nothing is computed twice.
+template <int R, int LANES, bool DELTA>
+__device__ __forceinline__ float lr_walk_token(float (&S)[R], const float* sk, const float* sq, const float* sg, float lam, float vv,
+                                               float beta, float qk, int sub) {
+    float kr[R];
+    float kS[2] = {0.0f, 0.0f}, qS[2] = {0.0f, 0.0f};
 #pragma unroll
     for (int i = 0; i < R / 4; ++i) {
-        const int at = i * 32 + sub * 4;
+        const int at = i * 4 * LANES + sub * 4;
         const float4 k4 = *reinterpret_cast<const float4*>(sk + at);
         const float4 q4 = *reinterpret_cast<const float4*>(sq + at);
-        t.k[i * 4] = k4.x; t.k[i * 4 + 1] = k4.y; t.k[i * 4 + 2] = k4.z; t.k[i * 4 + 3] = k4.w;
-        t.q[i * 4] = q4.x; t.q[i * 4 + 1] = q4.y; t.q[i * 4 + 2] = q4.z; t.q[i * 4 + 3] = q4.w;
-        if (DELTA) {
-            const float4 g4 = *reinterpret_cast<const float4*>(sg + at);
-            t.g[i * 4] = g4.x; t.g[i * 4 + 1] = g4.y; t.g[i * 4 + 2] = g4.z; t.g[i * 4 + 3] = g4.w;
+        float4 g4 = make_float4(lam, lam, lam, lam);
+        if (DELTA) g4 = *reinterpret_cast<const float4*>(sg + at);
+        const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w}, gg[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float s = S[i * 4 + e] * gg[e];
+            S[i * 4 + e] = s;
+            kr[i * 4 + e] = kk[e];
+            if (DELTA) kS[i & 1] = fmaf(kk[e], s, kS[i & 1]);
+            qS[i & 1] = fmaf(qq[e], s, qS[i & 1]);
         }
     }
-    t.v = vv; t.beta = beta; t.qk = qk;
-}
-
-// Returns the column's output on all eight lanes.  With S the state before the token:
-//   delta  u = beta (v - sum (k g) S);  o = sum (q g) S + (q . k) u;  S <- g S + k u
-//   decay  o = lambda sum q S + (q . k) v;                            S <- lambda S + k v
-// so that only the sum over k (delta) lies between one token's state and the next one's: the products with g and the sum
-// over q wait for nothing but S.
-template <int R, bool DELTA>
-__device__ __forceinline__ float lr_walk_token(float (&S)[R], const LrTok<R, DELTA>& t, float lam) {
-    float ks[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float ks = kS[0] + kS[1], qs = qS[0] + qS[1];
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-        if (DELTA) {
-            ks[i & 3] = fmaf(t.k[i] * t.g[i], S[i], ks[i & 3]);
-            qs[i & 3] = fmaf(t.q[i] * t.g[i], S[i], qs[i & 3]);
-        } else {
-            qs[i & 3] = fmaf(t.q[i], S[i], qs[i & 3]);
-        }
+    for (int o = 1; o < LANES; o <<= 1) {
+        if (DELTA) ks += __shfl_xor_sync(0xffffffffu, ks, o);
+        qs += __shfl_xor_sync(0xffffffffu, qs, o);
     }
-    float kss = (ks[0] + ks[1]) + (ks[2] + ks[3]), qss = (qs[0] + qs[1]) + (qs[2] + qs[3]);
+    const float u = DELTA ? beta * (vv - ks) : vv;
 #pragma unroll
-    for (int o = 1; o < 8; o <<= 1) {
-        if (DELTA) kss += __shfl_xor_sync(0xffffffffu, kss, o);
-        qss += __shfl_xor_sync(0xffffffffu, qss, o);
-    }
-    if (DELTA) {
-        const float u = t.beta * (t.v - kss);
-#pragma unroll
-        for (int i = 0; i < R; ++i) S[i] = fmaf(t.k[i], u, t.g[i] * S[i]);
-        return fmaf(t.qk, u, qss);
-    } else {
-#pragma unroll
-        for (int i = 0; i < R; ++i) S[i] = fmaf(t.k[i], t.v, lam * S[i]);
-        return fmaf(t.qk, t.v, lam * qss);
-    }
+    for (int i = 0; i < R; ++i) S[i] = fmaf(kr[i], u, S[i]);
+    return fmaf(qk, u, qs);
 }
 
 // ---- the walk that makes its own inputs ready (steps of single tokens) -----------------------------------------------------
-// DP = 8 * R >= dim; what lies past dim is zero.
-template <typename T, int R, bool DELTA>
-__global__ void __launch_bounds__(LR_THREADS)
+// DP = LANES * R >= dim; what lies past dim is zero.
+template <typename T, int R, int LANES, int COLS, bool DELTA>
+__global__ void __launch_bounds__(COLS * LANES)
 linear_state_kernel(const LinearStateArgs p, int tiles) {
-    constexpr int DP = 8 * R;
+    constexpr int DP = LANES * R, NT = COLS * LANES;
     extern __shared__ float smem[];
     float* sq = smem;                              // [LR_CHUNK][DP]
     float* sk = sq + LR_CHUNK * DP;                // [LR_CHUNK][DP]
     float* sg = sk + LR_CHUNK * DP;                // [LR_CHUNK][DP]   (delta only)
-    float* sv = sg + (DELTA ? LR_CHUNK * DP : 0);  // [LR_CHUNK][LR_COLS]
-    float* sbeta = sv + LR_CHUNK * LR_COLS;        // [LR_CHUNK]
+    float* sv = sg + (DELTA ? LR_CHUNK * DP : 0);  // [LR_CHUNK][COLS]
+    float* sbeta = sv + LR_CHUNK * COLS;        // [LR_CHUNK]
     float* sqk = sbeta + LR_CHUNK;                 // [LR_CHUNK]
     const int seg = blockIdx.x / tiles, tile = blockIdx.x - seg * tiles, h = blockIdx.y;
     const int kvh = h / (p.heads / p.kv_heads);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane & 7;
-    const int col = tile * LR_COLS + (threadIdx.x >> 3);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = threadIdx.x % LANES;
+    const int col = tile * COLS + threadIdx.x / LANES;
     const bool live = col < p.vdim;
     const int t0 = p.bounds ? p.bounds[2 * seg] : seg, t1 = p.bounds ? p.bounds[2 * seg + 1] : seg + 1;
     const int slot = p.slots[seg];
@@ -168,7 +148,7 @@ linear_state_kernel(const LinearStateArgs p, int tiles) {
     for (int i = 0; i < R / 4; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int d = i * 32 + sub * 4 + e;
+            const int d = i * 4 * LANES + sub * 4 + e;
             S[i * 4 + e] = (srow && d < dim) ? srow[d] : 0.0f;
         }
     const float lam = DELTA ? 0.0f : p.decay[h];
@@ -178,7 +158,7 @@ linear_state_kernel(const LinearStateArgs p, int tiles) {
         const int cnt = min(LR_CHUNK, t1 - c0);
         __syncthreads();                                                   // the last chunk has been walked
         // ---- stage: q, k (unit vectors in the delta rule), the decays, q . k; a warp per token
-        for (int tt = warp; tt < cnt; tt += LR_THREADS / 32) {
+        for (int tt = warp; tt < cnt; tt += NT / 32) {
             const size_t n = (size_t)(c0 + tt);
             const float dot = lr_ready_qk<T, DP, DELTA>(q + n * p.ldq + (size_t)kvh * dim, k + n * p.ldk + (size_t)kvh * dim, dim,
                                                         p.act_silu, p.q_scale, p.unit_eps, lane, sq + tt * DP, sk + tt * DP);
@@ -194,8 +174,8 @@ linear_state_kernel(const LinearStateArgs p, int tiles) {
                 sbeta[tt] = DELTA ? lr_sigmoid(to_f32<T>(b[n * p.ldb + h])) : 1.0f;
             }
         }
-        for (int idx = threadIdx.x; idx < cnt * LR_COLS; idx += LR_THREADS) {
-            const int tt = idx / LR_COLS, c = tile * LR_COLS + (idx - tt * LR_COLS);
+        for (int idx = threadIdx.x; idx < cnt * COLS; idx += NT) {
+            const int tt = idx / COLS, c = tile * COLS + (idx - tt * COLS);
             float x = c < vdim ? to_f32<T>(v[(size_t)(c0 + tt) * p.ldv + (size_t)h * vdim + c]) : 0.0f;
             if (p.act_silu) x = lr_silu(x);
             sv[idx] = x;
@@ -203,9 +183,8 @@ linear_state_kernel(const LinearStateArgs p, int tiles) {
         __syncthreads();
         // ---- walk
         for (int tt = 0; tt < cnt; ++tt) {
-            LrTok<R, DELTA> tok;
-            lr_load_token<R, DELTA>(tok, sk + tt * DP, sq + tt * DP, sg + tt * DP, sv[tt * LR_COLS + (threadIdx.x >> 3)], sbeta[tt], sqk[tt], sub);
-            const float o = lr_walk_token<R, DELTA>(S, tok, lam);
+            const float o = lr_walk_token<R, LANES, DELTA>(S, sk + tt * DP, sq + tt * DP, sg + tt * DP, lam, sv[tt * COLS + threadIdx.x / LANES],
+                                                           sbeta[tt], sqk[tt], sub);
             if (sub == 0 && live) p.y[(size_t)(c0 + tt) * ((size_t)p.heads * vdim) + (size_t)h * vdim + col] = o;
         }
     }
@@ -214,24 +193,24 @@ linear_state_kernel(const LinearStateArgs p, int tiles) {
         for (int i = 0; i < R / 4; ++i)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int d = i * 32 + sub * 4 + e;
+                const int d = i * 4 * LANES + sub * 4 + e;
                 if (d < dim) srow[d] = S[i * 4 + e];
             }
     }
 }
 
-template <typename T, int R, bool DELTA>
+template <typename T, int R, int LANES, int COLS, bool DELTA>
 static int launch_linear_state(const LinearStateArgs& p, cudaStream_t stream) {
-    const int tiles = (p.vdim + LR_COLS - 1) / LR_COLS;
-    const size_t smem = ((size_t)LR_CHUNK * 8 * R * (DELTA ? 3 : 2) + LR_CHUNK * LR_COLS + 2 * LR_CHUNK) * sizeof(float);
+    const int tiles = (p.vdim + COLS - 1) / COLS;
+    const size_t smem = ((size_t)LR_CHUNK * LANES * R * (DELTA ? 3 : 2) + LR_CHUNK * COLS + 2 * LR_CHUNK) * sizeof(float);
     if (smem > 48 * 1024) {
         static bool raised = false;       // per instantiation
         if (!raised) {
-            cudaFuncSetAttribute(linear_state_kernel<T, R, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(linear_state_kernel<T, R, LANES, COLS, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             raised = true;
         }
     }
-    linear_state_kernel<T, R, DELTA><<<dim3((unsigned)(p.n_segments * tiles), (unsigned)p.heads), LR_THREADS, smem, stream>>>(p, tiles);
+    linear_state_kernel<T, R, LANES, COLS, DELTA><<<dim3((unsigned)(p.n_segments * tiles), (unsigned)p.heads), COLS * LANES, smem, stream>>>(p, tiles);
     return zi_check_launch("linear_state");
 }
 
@@ -239,15 +218,15 @@ static int launch_linear_state(const LinearStateArgs& p, cudaStream_t stream) {
 // Making a token ready (loads from global memory, unit vectors, softplus and exponentials) does not depend on the state, so
 // for long segments it runs first, over all tokens and heads at once, and leaves per token and head one record of float32
 //   [ q DP | k DP | g DP (delta) | beta, q . k, 0, 0 ]
-// and the values [tiles * LR_COLS] (SiLU applied where asked, zero past vdim).  The walk then only copies records into
+// and the values [tiles * COLS] (SiLU applied where asked, zero past vdim).  The walk then only copies records into
 // shared memory, two chunks in flight, and walks.  Both forms call the same functions on a token, so its result has the
 // same bits in either.
 template <bool DELTA, int DP> struct LrRecord { static constexpr int SIZE = (DELTA ? 3 : 2) * DP + 4; };
 
-template <typename T, int R, bool DELTA>
+template <typename T, int DP, bool DELTA>
 __global__ void __launch_bounds__(LR_THREADS)
 linear_state_ready_kernel(const LinearStateArgs p, float* __restrict__ rec, float* __restrict__ pv, int n_tokens, int vp) {
-    constexpr int DP = 8 * R, REC = LrRecord<DELTA, DP>::SIZE;
+    constexpr int REC = LrRecord<DELTA, DP>::SIZE;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long pair = (long long)blockIdx.x * (LR_THREADS / 32) + warp;
     if (pair >= (long long)n_tokens * p.heads) return;
@@ -283,20 +262,19 @@ __device__ __forceinline__ void lr_copy16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(src) : "memory");
 }
 
-template <int R, bool DELTA>
-__global__ void __launch_bounds__(LR_THREADS)
+template <int R, int LANES, int COLS, bool DELTA>
+__global__ void __launch_bounds__(COLS * LANES)
 linear_state_walk_kernel(const LinearStateArgs p, const float* __restrict__ rec, const float* __restrict__ pv, int tiles) {
-    constexpr int DP = 8 * R, REC = LrRecord<DELTA, DP>::SIZE;
-    constexpr int STAGE = LR_CHUNK * (REC + LR_COLS);                      // a chunk's records, then its values
-    constexpr bool PIPE = R <= 16;                                         // a second token's registers fit
+    constexpr int DP = LANES * R, NT = COLS * LANES, REC = LrRecord<DELTA, DP>::SIZE;
+    constexpr int STAGE = LR_CHUNK * (REC + COLS);                      // a chunk's records, then its values
     extern __shared__ __align__(16) float smem[];
     const int seg = blockIdx.x / tiles, tile = blockIdx.x - seg * tiles, h = blockIdx.y;
-    const int sub = threadIdx.x & 7;
-    const int col = tile * LR_COLS + (threadIdx.x >> 3);
+    const int sub = threadIdx.x % LANES;
+    const int col = tile * COLS + threadIdx.x / LANES;
     const bool live = col < p.vdim;
     const int t0 = p.bounds ? p.bounds[2 * seg] : seg, t1 = p.bounds ? p.bounds[2 * seg + 1] : seg + 1;
     const int slot = p.slots[seg];
-    const int dim = p.dim, vdim = p.vdim, vp = tiles * LR_COLS;
+    const int dim = p.dim, vdim = p.vdim, vp = tiles * COLS;
 
     float S[R];
     float* srow = (slot >= 0 && live) ? p.state + (size_t)slot * p.slot_stride + ((size_t)h * vdim + col) * dim : nullptr;
@@ -304,20 +282,20 @@ linear_state_walk_kernel(const LinearStateArgs p, const float* __restrict__ rec,
     for (int i = 0; i < R / 4; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const int d = i * 32 + sub * 4 + e;
+            const int d = i * 4 * LANES + sub * 4 + e;
             S[i * 4 + e] = (srow && d < dim) ? srow[d] : 0.0f;
         }
     const float lam = DELTA ? 0.0f : p.decay[h];
 
     auto fetch = [&](int c0, float* dst) {
         const int cnt = min(LR_CHUNK, t1 - c0);
-        for (int idx = threadIdx.x; idx < cnt * (REC / 4); idx += LR_THREADS) {
+        for (int idx = threadIdx.x; idx < cnt * (REC / 4); idx += NT) {
             const int tt = idx / (REC / 4), g = idx - tt * (REC / 4);
             lr_copy16(dst + tt * REC + g * 4, rec + ((size_t)(c0 + tt) * p.heads + h) * REC + g * 4);
         }
-        for (int idx = threadIdx.x; idx < cnt * (LR_COLS / 4); idx += LR_THREADS) {
-            const int tt = idx / (LR_COLS / 4), g = idx - tt * (LR_COLS / 4);
-            lr_copy16(dst + LR_CHUNK * REC + tt * LR_COLS + g * 4, pv + ((size_t)(c0 + tt) * p.heads + h) * vp + tile * LR_COLS + g * 4);
+        for (int idx = threadIdx.x; idx < cnt * (COLS / 4); idx += NT) {
+            const int tt = idx / (COLS / 4), g = idx - tt * (COLS / 4);
+            lr_copy16(dst + LR_CHUNK * REC + tt * COLS + g * 4, pv + ((size_t)(c0 + tt) * p.heads + h) * vp + tile * COLS + g * 4);
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
@@ -334,34 +312,12 @@ linear_state_walk_kernel(const LinearStateArgs p, const float* __restrict__ rec,
         }
         __syncthreads();                                                   // everyone's copies of this chunk have landed
         const float* st = smem + s * STAGE;
-        const float* sv = st + LR_CHUNK * REC + (threadIdx.x >> 3);
+        const float* sv = st + LR_CHUNK * REC + threadIdx.x / LANES;
         float* yc = p.y + (size_t)c0 * ((size_t)p.heads * vdim) + (size_t)h * vdim + col;
-        auto load = [&](LrTok<R, DELTA>& t, int tt) {
+        for (int tt = 0; tt < cnt; ++tt) {
             const float* r = st + tt * REC;
-            lr_load_token<R, DELTA>(t, r + DP, r, r + 2 * DP, sv[tt * LR_COLS], r[REC - 4], r[REC - 3], sub);
-        };
-        if (PIPE) {
-            // two tokens by turns: one's loads are in flight while the other walks
-            LrTok<R, DELTA> ta, tb;
-            load(ta, 0);
-            for (int tt = 0; tt < cnt; tt += 2) {
-                const bool second = tt + 1 < cnt;
-                if (second) load(tb, tt + 1);
-                const float oa = lr_walk_token<R, DELTA>(S, ta, lam);
-                if (sub == 0 && live) yc[(size_t)tt * ((size_t)p.heads * vdim)] = oa;
-                if (second) {
-                    if (tt + 2 < cnt) load(ta, tt + 2);
-                    const float ob = lr_walk_token<R, DELTA>(S, tb, lam);
-                    if (sub == 0 && live) yc[(size_t)(tt + 1) * ((size_t)p.heads * vdim)] = ob;
-                }
-            }
-        } else {
-            for (int tt = 0; tt < cnt; ++tt) {
-                LrTok<R, DELTA> tok;
-                load(tok, tt);
-                const float o = lr_walk_token<R, DELTA>(S, tok, lam);
-                if (sub == 0 && live) yc[(size_t)tt * ((size_t)p.heads * vdim)] = o;
-            }
+            const float o = lr_walk_token<R, LANES, DELTA>(S, r + DP, r, r + 2 * DP, lam, sv[tt * COLS], r[REC - 4], r[REC - 3], sub);
+            if (sub == 0 && live) yc[(size_t)tt * ((size_t)p.heads * vdim)] = o;
         }
         __syncthreads();                                                   // this chunk's buffer may be filled again
     }
@@ -370,39 +326,40 @@ linear_state_walk_kernel(const LinearStateArgs p, const float* __restrict__ rec,
         for (int i = 0; i < R / 4; ++i)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int d = i * 32 + sub * 4 + e;
+                const int d = i * 4 * LANES + sub * 4 + e;
                 if (d < dim) srow[d] = S[i * 4 + e];
             }
     }
 }
 
-template <typename T, int R, bool DELTA>
+template <typename T, int R, int LANES, int COLS, bool DELTA>
 static int launch_linear_state_ready(const LinearStateArgs& p, float* work, int n_tokens, cudaStream_t stream) {
-    constexpr int REC = LrRecord<DELTA, 8 * R>::SIZE;
-    const int tiles = (p.vdim + LR_COLS - 1) / LR_COLS, vp = tiles * LR_COLS;
+    constexpr int REC = LrRecord<DELTA, LANES * R>::SIZE;
+    const int tiles = (p.vdim + COLS - 1) / COLS, vp = tiles * COLS;
     const long long pairs = (long long)n_tokens * p.heads;
     float* rec = work;
     float* pv = work + (size_t)pairs * REC;
     const long long blocks = (pairs + LR_THREADS / 32 - 1) / (LR_THREADS / 32);
     if (blocks > 2147483647LL) return zi_fail("linear_state: %lld tokens x heads are too many for one step", pairs);
-    linear_state_ready_kernel<T, R, DELTA><<<(unsigned)blocks, LR_THREADS, 0, stream>>>(p, rec, pv, n_tokens, vp);
+    linear_state_ready_kernel<T, LANES * R, DELTA><<<(unsigned)blocks, LR_THREADS, 0, stream>>>(p, rec, pv, n_tokens, vp);
     if (int rc = zi_check_launch("linear_state_ready")) return rc;
-    const size_t smem = (size_t)2 * LR_CHUNK * (REC + LR_COLS) * sizeof(float);
+    const size_t smem = (size_t)2 * LR_CHUNK * (REC + COLS) * sizeof(float);
     if (smem > 48 * 1024) {
         static bool raised = false;       // per instantiation
         if (!raised) {
-            cudaFuncSetAttribute(linear_state_walk_kernel<R, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(linear_state_walk_kernel<R, LANES, COLS, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             raised = true;
         }
     }
-    linear_state_walk_kernel<R, DELTA><<<dim3((unsigned)(p.n_segments * tiles), (unsigned)p.heads), LR_THREADS, smem, stream>>>(p, rec, pv, tiles);
+    linear_state_walk_kernel<R, LANES, COLS, DELTA><<<dim3((unsigned)(p.n_segments * tiles), (unsigned)p.heads), COLS * LANES, smem, stream>>>(p, rec, pv, tiles);
     return zi_check_launch("linear_state_walk");
 }
 
 // floats of workspace the form with inputs made ready needs for a step
 static long long linear_state_work_floats(int rule, int n_tokens, int heads, int dim, int vdim) {
     const int dp = dim <= 32 ? 32 : dim <= 64 ? 64 : dim <= 128 ? 128 : 256;
-    const int rec = (rule == 0 ? 3 : 2) * dp + 4, vp = (vdim + LR_COLS - 1) / LR_COLS * LR_COLS;
+    const int cols = LR_COLS;
+    const int rec = (rule == 0 ? 3 : 2) * dp + 4, vp = (vdim + cols - 1) / cols * cols;
     return (long long)n_tokens * heads * (rec + vp);
 }
 
@@ -412,18 +369,18 @@ ZI_EXPORT long long zi_linear_state_work_floats(int rule, int n_tokens, int head
 
 template <typename T, bool DELTA>
 static int pick_linear_state_ready(const LinearStateArgs& p, float* work, int n_tokens, cudaStream_t stream) {
-    if (p.dim <= 32) return launch_linear_state_ready<T, 4, DELTA>(p, work, n_tokens, stream);
-    if (p.dim <= 64) return launch_linear_state_ready<T, 8, DELTA>(p, work, n_tokens, stream);
-    if (p.dim <= 128) return launch_linear_state_ready<T, 16, DELTA>(p, work, n_tokens, stream);
-    return launch_linear_state_ready<T, 32, DELTA>(p, work, n_tokens, stream);
+    if (p.dim <= 32) return launch_linear_state_ready<T, 4, LR_LANES, LR_COLS, DELTA>(p, work, n_tokens, stream);
+    if (p.dim <= 64) return launch_linear_state_ready<T, 8, LR_LANES, LR_COLS, DELTA>(p, work, n_tokens, stream);
+    if (p.dim <= 128) return launch_linear_state_ready<T, 16, LR_LANES, LR_COLS, DELTA>(p, work, n_tokens, stream);
+    return launch_linear_state_ready<T, 32, LR_LANES, LR_COLS, DELTA>(p, work, n_tokens, stream);
 }
 
 template <typename T, bool DELTA>
 static int pick_linear_state(const LinearStateArgs& p, cudaStream_t stream) {
-    if (p.dim <= 32) return launch_linear_state<T, 4, DELTA>(p, stream);
-    if (p.dim <= 64) return launch_linear_state<T, 8, DELTA>(p, stream);
-    if (p.dim <= 128) return launch_linear_state<T, 16, DELTA>(p, stream);
-    return launch_linear_state<T, 32, DELTA>(p, stream);
+    if (p.dim <= 32) return launch_linear_state<T, 4, LR_LANES, LR_COLS, DELTA>(p, stream);
+    if (p.dim <= 64) return launch_linear_state<T, 8, LR_LANES, LR_COLS, DELTA>(p, stream);
+    if (p.dim <= 128) return launch_linear_state<T, 16, LR_LANES, LR_COLS, DELTA>(p, stream);
+    return launch_linear_state<T, 32, LR_LANES, LR_COLS, DELTA>(p, stream);
 }
 
 ZI_EXPORT int zi_linear_state(int rule, const void* q, long long ldq, const void* k, long long ldk, const void* v, long long ldv,
