@@ -80,15 +80,18 @@ __device__ __forceinline__ float lr_decay(float a, float dt_bias, float rate) { 
 // One token through the R entries a thread holds of its column.  A column is shared by LANES lanes; a thread holds entries
 // i * 4 LANES + sub * 4 + e (i < R / 4, e < 4), sub = lane % LANES, so that the lanes of a column read consecutive bytes of
 // a staged vector and the columns of a warp read it as one broadcast; sk, sq, sg: the token's staged key, query and decays
-// (R LANES floats each; what lies past dim is zero).  Returns the column's output, o = q . S after the write
-// = q . (g S) + (q . k) u, on all lanes of the column.  The walk's time is its instruction count (a warp alone on its
-// scheduler issues every third cycle or so), so a token costs four instructions per entry in the delta rule and three with
-// a constant decay, and nothing is computed twice.
+// (R LANES floats each; what lies past dim is zero).  The column's output is o = q . S after the write
+// = q . (g S) + (q . k) u.
+//
+// A token's walk comes in two halves, for callers that take several tokens in one stretch of straight-line code: the read-outs'
+// sums over the lanes wait for one another side by side at the end, and a token's loads and products stand before the
+// sums of the token before it.  Only the sum over k of the delta rule lies between one token's state and the next one's.
+// lr_walk_token is the two halves and the sums for one token, so a token has the same bits whoever walks it.  The sums
+// within a thread run in four chains (entry e of every group of four), which keeps consecutive instructions independent.
 template <int R, int LANES, bool DELTA>
-__device__ __forceinline__ float lr_walk_token(float (&S)[R], const float* sk, const float* sq, const float* sg, float lam, float vv,
-                                               float beta, float qk, int sub) {
-    float kr[R];
-    float kS[2] = {0.0f, 0.0f}, qS[2] = {0.0f, 0.0f};
+__device__ __forceinline__ void lr_token_local(float (&S)[R], float (&kr)[R], const float* sk, const float* sq, const float* sg, float lam,
+                                               int sub, float& ks, float& qs) {
+    float kS[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qS[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int i = 0; i < R / 4; ++i) {
         const int at = i * 4 * LANES + sub * 4;
@@ -102,19 +105,35 @@ __device__ __forceinline__ float lr_walk_token(float (&S)[R], const float* sk, c
             const float s = S[i * 4 + e] * gg[e];
             S[i * 4 + e] = s;
             kr[i * 4 + e] = kk[e];
-            if (DELTA) kS[i & 1] = fmaf(kk[e], s, kS[i & 1]);
-            qS[i & 1] = fmaf(qq[e], s, qS[i & 1]);
+            if (DELTA) kS[e] = fmaf(kk[e], s, kS[e]);
+            qS[e] = fmaf(qq[e], s, qS[e]);
         }
     }
-    float ks = kS[0] + kS[1], qs = qS[0] + qS[1];
-#pragma unroll
-    for (int o = 1; o < LANES; o <<= 1) {
-        if (DELTA) ks += __shfl_xor_sync(0xffffffffu, ks, o);
-        qs += __shfl_xor_sync(0xffffffffu, qs, o);
-    }
-    const float u = DELTA ? beta * (vv - ks) : vv;
+    ks = (kS[0] + kS[1]) + (kS[2] + kS[3]);
+    qs = (qS[0] + qS[1]) + (qS[2] + qS[3]);
+}
+
+template <int R>
+__device__ __forceinline__ void lr_token_write(float (&S)[R], const float (&kr)[R], float u) {
 #pragma unroll
     for (int i = 0; i < R; ++i) S[i] = fmaf(kr[i], u, S[i]);
+}
+
+// Returns the column's output on all its lanes.
+template <int R, int LANES, bool DELTA>
+__device__ __forceinline__ float lr_walk_token(float (&S)[R], const float* sk, const float* sq, const float* sg, float lam, float vv,
+                                               float beta, float qk, int sub) {
+    float kr[R], ks, qs;
+    lr_token_local<R, LANES, DELTA>(S, kr, sk, sq, sg, lam, sub, ks, qs);
+    float u = vv;
+    if (DELTA) {
+#pragma unroll
+        for (int o = 1; o < LANES; o <<= 1) ks += __shfl_xor_sync(0xffffffffu, ks, o);
+        u = beta * (vv - ks);
+    }
+    lr_token_write<R>(S, kr, u);
+#pragma unroll
+    for (int o = 1; o < LANES; o <<= 1) qs += __shfl_xor_sync(0xffffffffu, qs, o);
     return fmaf(qk, u, qs);
 }
 
@@ -314,7 +333,33 @@ linear_state_walk_kernel(const LinearStateArgs p, const float* __restrict__ rec,
         const float* st = smem + s * STAGE;
         const float* sv = st + LR_CHUNK * REC + threadIdx.x / LANES;
         float* yc = p.y + (size_t)c0 * ((size_t)p.heads * vdim) + (size_t)h * vdim + col;
-        for (int tt = 0; tt < cnt; ++tt) {
+        int tt = 0;
+        // four tokens at a time, in straight-line code
+        for (; tt + 4 <= cnt; tt += 4) {
+            float qs[4], u[4], qk[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float* r = st + (tt + j) * REC;
+                float kr[R], ks;
+                lr_token_local<R, LANES, DELTA>(S, kr, r + DP, r, r + 2 * DP, lam, sub, ks, qs[j]);
+                u[j] = sv[(tt + j) * COLS];
+                qk[j] = r[REC - 3];
+                if (DELTA) {
+#pragma unroll
+                    for (int o = 1; o < LANES; o <<= 1) ks += __shfl_xor_sync(0xffffffffu, ks, o);
+                    u[j] = r[REC - 4] * (u[j] - ks);
+                }
+                lr_token_write<R>(S, kr, u[j]);
+            }
+#pragma unroll
+            for (int o = 1; o < LANES; o <<= 1)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) qs[j] += __shfl_xor_sync(0xffffffffu, qs[j], o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (sub == 0 && live) yc[(size_t)(tt + j) * ((size_t)p.heads * vdim)] = fmaf(qk[j], u[j], qs[j]);
+        }
+        for (; tt < cnt; ++tt) {
             const float* r = st + tt * REC;
             const float o = lr_walk_token<R, LANES, DELTA>(S, r + DP, r, r + 2 * DP, lam, sv[tt * COLS], r[REC - 4], r[REC - 3], sub);
             if (sub == 0 && live) yc[(size_t)tt * ((size_t)p.heads * vdim)] = o;
