@@ -356,13 +356,13 @@ def kevatar_config(width, heads, ff, window, layers, vocab, dim=128, **_):
     turned with stretched frequencies, scores capped, recurrent heads of 128 x 128 with low ranks of 64, four taps, and a
     per-token table of 64 columns a layer."""
     kv = 2 if heads <= 12 else 4
-    rot = {"base": 1000000.0, "dims": dim // 2, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}
+    rot = {"base": 500000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "original": 2048, "fast": 16.0, "slow": 2.0}}
     out = []
     for i in range(layers):
         kind = i % 4
         if kind in (0, 3):
             m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": window}, "rot": rot,
-                 "scale": dim ** -0.5, "softcap": 30.0}
+                 "scale": dim ** -0.5, "softcap": 50.0}
             if kind == 3:
                 m["kv_from"] = i - 3
             out.append({"type": "attention", "mixer": m})
@@ -373,7 +373,7 @@ def kevatar_config(width, heads, ff, window, layers, vocab, dim=128, **_):
             out.append({"type": "lightning", "mixer": {"heads": heads, "dim": dim, "vdim": dim,
                                                        "decay": [1.0 - 2.0 ** -(2 + 6 * h / max(1, heads - 1)) for h in range(heads)]}})
         out[-1]["mlp"] = {"kind": "dense", "ff": (2 * ff // 3 + 7) // 8 * 8}
-    return {"architecture": "Kevatar", "vocab": vocab, "width": width, "max_positions": CONTEXT, "norm": {"eps": 1e-6},
+    return {"architecture": "Kevatar", "vocab": vocab, "width": width, "max_positions": CONTEXT, "norm": {"eps": 1e-5},
             "embedding": {"scale": float(width) ** 0.5}, "token_side": {"dim": 64}, "layers": out}
 
 

@@ -22,7 +22,8 @@ ZI_DEFINE_LAST_ERROR(linrec)
 #define LR_LANES 8               // lanes that share a column of S
 #define LR_COLS 16               // columns of S per block.  Measured on 2,048 tokens of 12 heads of 128 x 128: 8, 16 or 32 lanes
                                  // with 4 to 64 columns per block all take 0.5 to 1.3 ms; this one is the quickest
-#define LR_CHUNK 16              // tokens staged in shared memory at a time
+#define LR_CHUNK 16              // tokens staged in shared memory at a time by the walk that makes its own inputs ready
+#define LR_WALK_CHUNK 32         // and by the walk over records (two such chunks are in shared memory)
 
 struct LinearStateArgs {
     const void* q; const void* k; const void* v; const void* a; const void* b;
@@ -285,7 +286,7 @@ template <int R, int LANES, int COLS, bool DELTA>
 __global__ void __launch_bounds__(COLS * LANES)
 linear_state_walk_kernel(const LinearStateArgs p, const float* __restrict__ rec, const float* __restrict__ pv, int tiles) {
     constexpr int DP = LANES * R, NT = COLS * LANES, REC = LrRecord<DELTA, DP>::SIZE;
-    constexpr int STAGE = LR_CHUNK * (REC + COLS);                      // a chunk's records, then its values
+    constexpr int STAGE = LR_WALK_CHUNK * (REC + COLS);                      // a chunk's records, then its values
     extern __shared__ __align__(16) float smem[];
     const int seg = blockIdx.x / tiles, tile = blockIdx.x - seg * tiles, h = blockIdx.y;
     const int sub = threadIdx.x % LANES;
@@ -307,31 +308,31 @@ linear_state_walk_kernel(const LinearStateArgs p, const float* __restrict__ rec,
     const float lam = DELTA ? 0.0f : p.decay[h];
 
     auto fetch = [&](int c0, float* dst) {
-        const int cnt = min(LR_CHUNK, t1 - c0);
+        const int cnt = min(LR_WALK_CHUNK, t1 - c0);
         for (int idx = threadIdx.x; idx < cnt * (REC / 4); idx += NT) {
             const int tt = idx / (REC / 4), g = idx - tt * (REC / 4);
             lr_copy16(dst + tt * REC + g * 4, rec + ((size_t)(c0 + tt) * p.heads + h) * REC + g * 4);
         }
         for (int idx = threadIdx.x; idx < cnt * (COLS / 4); idx += NT) {
             const int tt = idx / (COLS / 4), g = idx - tt * (COLS / 4);
-            lr_copy16(dst + LR_CHUNK * REC + tt * COLS + g * 4, pv + ((size_t)(c0 + tt) * p.heads + h) * vp + tile * COLS + g * 4);
+            lr_copy16(dst + LR_WALK_CHUNK * REC + tt * COLS + g * 4, pv + ((size_t)(c0 + tt) * p.heads + h) * vp + tile * COLS + g * 4);
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
 
     if (t0 < t1) fetch(t0, smem);
     int s = 0;
-    for (int c0 = t0; c0 < t1; c0 += LR_CHUNK, s ^= 1) {
-        const int cnt = min(LR_CHUNK, t1 - c0);
-        if (c0 + LR_CHUNK < t1) {
-            fetch(c0 + LR_CHUNK, smem + (s ^ 1) * STAGE);
+    for (int c0 = t0; c0 < t1; c0 += LR_WALK_CHUNK, s ^= 1) {
+        const int cnt = min(LR_WALK_CHUNK, t1 - c0);
+        if (c0 + LR_WALK_CHUNK < t1) {
+            fetch(c0 + LR_WALK_CHUNK, smem + (s ^ 1) * STAGE);
             asm volatile("cp.async.wait_group 1;\n" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
         __syncthreads();                                                   // everyone's copies of this chunk have landed
         const float* st = smem + s * STAGE;
-        const float* sv = st + LR_CHUNK * REC + threadIdx.x / LANES;
+        const float* sv = st + LR_WALK_CHUNK * REC + threadIdx.x / LANES;
         float* yc = p.y + (size_t)c0 * ((size_t)p.heads * vdim) + (size_t)h * vdim + col;
         int tt = 0;
         // four tokens at a time, in straight-line code
@@ -388,7 +389,7 @@ static int launch_linear_state_ready(const LinearStateArgs& p, float* work, int 
     if (blocks > 2147483647LL) return zi_fail("linear_state: %lld tokens x heads are too many for one step", pairs);
     linear_state_ready_kernel<T, LANES * R, DELTA><<<(unsigned)blocks, LR_THREADS, 0, stream>>>(p, rec, pv, n_tokens, vp);
     if (int rc = zi_check_launch("linear_state_ready")) return rc;
-    const size_t smem = (size_t)2 * LR_CHUNK * (REC + COLS) * sizeof(float);
+    const size_t smem = (size_t)2 * LR_WALK_CHUNK * (REC + COLS) * sizeof(float);
     if (smem > 48 * 1024) {
         static bool raised = false;       // per instantiation
         if (!raised) {
