@@ -4,7 +4,7 @@ spans from 2 entries to a whole head with and without stretched frequencies (ram
 above it), windows from 3 keys to none, layers that read another layer's keys through a window larger and smaller than the
 owner's, score caps and none, convolutions of 1 to 4 taps, low ranks that differ from one another and from the per-token
 table's width, models without that table, without a feed-forward in some layers, with an embedding scale and without, and
-models of recurrent layers alone (no paged cache) and of attention alone (no state slot)."""
+models of recurrent layers alone (no paged cache) and of attention alone (no state slot), and one of ones and extremes."""
 import copy
 import json
 import os
@@ -100,7 +100,20 @@ KV_E = {
         _with(_attn(2, 1, 16, 24, 64, _ROT_E, 0.4, kv_from=0), None),
     ],
 }
-CONFIGS = {"A": (KV_A, 41), "B": (KV_B, 42), "C": (KV_C, 43), "D": (KV_D, 44), "E": (KV_E, 45)}
+# ones and extremes: single heads everywhere, a window of one key (a token sees itself alone) read again through a window of
+# two, a whole head of 8 turned, a cap of 1 that bends every score, six taps, a key of 256 entries on the widest form of the
+# recurrence kernel beside one of 4, low ranks of 1, a table of one column, a decay of 1 (nothing fades) and one of 0
+# (nothing is kept)
+KV_F = {
+    "architecture": "Kevatar", "vocab": 64, "width": 48, "norm": {"eps": 1e-6}, "token_side": {"dim": 1},
+    "layers": [
+        _with(_attn(1, 1, 8, 8, 1, _rot(8, 10.0), 1.0, softcap=1.0), 8),
+        _with(_delta(1, 1, 256, 4, 6, 1, 1), 16),
+        _with(_lightning(2, 4, 4, (1.0, 0.0)), None),
+        _with(_attn(1, 1, 8, 8, 2, _rot(8, 10.0), 0.7, kv_from=0), 24),
+    ],
+}
+CONFIGS = {"A": (KV_A, 41), "B": (KV_B, 42), "C": (KV_C, 43), "D": (KV_D, 44), "E": (KV_E, 45), "F": (KV_F, 46)}
 INIT_SCALE = 5.0
 
 

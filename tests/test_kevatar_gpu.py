@@ -436,8 +436,8 @@ def judge(got, exp, dtype):
     assert all(e <= 4 * tol for e in errs.values()), max(errs.values())
 
 
-LENGTHS = {"A": [7, 13, 95, 45], "B": [1, 17, 120, 64], "C": [110, 5, 60], "D": [50, 2, 61], "E": [40, 3, 90]}
-PAGES = {"A": 4, "B": 16, "C": 8, "D": 8, "E": 16}
+LENGTHS = {"A": [7, 13, 95, 45], "B": [1, 17, 120, 64], "C": [110, 5, 60], "D": [50, 2, 61], "E": [40, 3, 90], "F": [33, 1, 70]}
+PAGES = {"A": 4, "B": 16, "C": 8, "D": 8, "E": 16, "F": 8}
 
 
 def test_layers_that_read_another_layer_s_keys_hold_no_cache(models):
@@ -456,7 +456,7 @@ def test_layers_that_read_another_layer_s_keys_hold_no_cache(models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 @pytest.mark.parametrize("family", ["whole", "tail", "chunks", "mixed"])
 def test_cuts_match_plain(models, name, dtype, family):
     """Whole prompts; a tail decoded token by token; portions down to two tokens; mixed batches of unequal requests in a
@@ -522,7 +522,7 @@ def test_long_decoding_and_the_first_tokens(models, dtype):
     judge(run_trace(core, steps), expected_logits(models["A"], requests), dtype)
 
 
-@pytest.mark.parametrize("name", ["A", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "C", "D", "F"])
 def test_float32_is_the_same_however_it_is_cut(models, name):
     """The same positions through four different schedules: the same bits (every float32 sum of the design has one order,
     which depends on constants alone; the recurrences run token by token whatever the portions)."""
@@ -537,7 +537,7 @@ def test_float32_is_the_same_however_it_is_cut(models, name):
         assert all(torch.equal(other[k], runs[0][k]) for k in runs[0])
 
 
-@pytest.mark.parametrize("name,graphs", [("A", False), ("A", True), ("B", True), ("C", False), ("D", True)])
+@pytest.mark.parametrize("name,graphs", [("A", False), ("A", True), ("B", True), ("C", False), ("D", True), ("F", True)])
 def test_greedy_generation_equals_plain(models, name, graphs):
     """Through the Python entry point and its scheduler: prompts in portions of five, a pool of pages and three state
     slots that the requests fill again, greedy tokens equal to the plain implementation's."""
