@@ -617,10 +617,50 @@ norm_add_kernel(float* __restrict__ h, const T* __restrict__ y, const TW* __rest
     }
 }
 
+// The same with eight entries per access; hidden a multiple of 8 and every pointer on a 16-byte boundary.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(NA_THREADS)
+norm_add_vec8_kernel(float* __restrict__ h, const T* __restrict__ y, const TW* __restrict__ w, T* __restrict__ rounded, float eps, int hidden) {
+    extern __shared__ float na_row[];
+    __shared__ float scratch[32];
+    const size_t n = blockIdx.x;
+    const T* yr = y + n * hidden;
+    float ss = 0.0f;
+    for (int j = threadIdx.x * 8; j < hidden; j += NA_THREADS * 8) {
+        float v[8];
+        load8(yr + j, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+        store8(na_row + j, v);
+    }
+    ss = block_sum(ss, scratch);
+    const float r = 1.0f / sqrtf(ss / (float)hidden + eps);
+    float* hr = h + n * hidden;
+    for (int j = threadIdx.x * 8; j < hidden; j += NA_THREADS * 8) {
+        float v[8], a[8], g[8];
+        load8(na_row + j, v);
+        load8(hr + j, a);
+        load8(w + j, g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) a[e] = a[e] + (v[e] * r) * g[e];
+        store8(hr + j, a);
+        if (rounded) store8(rounded + n * hidden + j, a);
+    }
+}
+
 ZI_EXPORT int zi_norm_add(float* h, const void* y, int dtype, const void* w, int w_dtype, void* rounded, float eps, int rows, int hidden,
                           cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (hidden <= 0 || (size_t)hidden * sizeof(float) > 48 * 1024) return zi_fail("norm_add: hidden=%d is not supported", hidden);
+    // which form runs depends on the sizes and on where the buffers start, never on the rows of the step
+    const bool vec = hidden % 8 == 0 && (((size_t)h | (size_t)y | (size_t)w | (size_t)rounded) & 15) == 0;
+    if (vec) {
+        ZI_DISPATCH(dtype, T, ZI_DISPATCH(w_dtype, TW, {
+            norm_add_vec8_kernel<T, TW><<<rows, NA_THREADS, (size_t)hidden * sizeof(float), stream>>>(h, (const T*)y, (const TW*)w, (T*)rounded,
+                                                                                                    eps, hidden);
+        }););
+        return zi_check_launch("norm_add");
+    }
     ZI_DISPATCH(dtype, T, ZI_DISPATCH(w_dtype, TW, {
         norm_add_kernel<T, TW><<<rows, NA_THREADS, (size_t)hidden * sizeof(float), stream>>>(h, (const T*)y, (const TW*)w, (T*)rounded, eps,
                                                                                            hidden);
