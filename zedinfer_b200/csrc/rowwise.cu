@@ -503,7 +503,7 @@ ZI_EXPORT int zi_sigmoid_mul(void* a, const void* g, int dtype, long long ldg, i
 // One block per token, one warp per head at a time; a head passes through the warp's stretch of shared memory, so the
 // sum of squares has one order whatever the step.
 // ---------------------------------------------------------------------------------------
-#define RN_WARPS 4
+#define RN_WARPS 8
 template <typename T>
 __global__ void __launch_bounds__(RN_WARPS * 32)
 rotary_norm_kernel(const T* __restrict__ x, long long ldx, T* __restrict__ q_out, T* __restrict__ cache, const int* __restrict__ tables,
