@@ -21,7 +21,7 @@ ZI_DEFINE_LAST_ERROR(moe)
 #define RT_MAX_PER_LANE 32            // experts <= 1024
 __global__ void __launch_bounds__(RT_WARPS * 32)
 route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top, int* __restrict__ idx,
-                  float* __restrict__ wts, int score) {
+                  float* __restrict__ wts, int score, const float* __restrict__ choice_bias) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * RT_WARPS + warp;
     if (t >= n_tokens) return;
@@ -33,6 +33,24 @@ route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts,
         v[i] = e < n_experts ? z[e] : -INFINITY;
     }
     float first = 0.0f, denom = 0.0f;
+    float zmax = 0.0f, zsum = 1.0f;
+    if (score == 2) {
+        // every expert's share of the softmax over all of them; the choice goes by share + choice_bias, the weight is the share
+        zmax = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < RT_MAX_PER_LANE; ++i) zmax = fmaxf(zmax, v[i]);
+        zmax = warp_max(zmax);
+        zsum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < RT_MAX_PER_LANE; ++i)
+            if (lane + 32 * i < n_experts) zsum += expf(v[i] - zmax);
+        zsum = warp_sum(zsum);
+#pragma unroll
+        for (int i = 0; i < RT_MAX_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e < n_experts) v[i] = expf(v[i] - zmax) / zsum + (choice_bias ? choice_bias[e] : 0.0f);
+        }
+    }
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY;
         int best_e = 0x7fffffff;
@@ -48,7 +66,7 @@ route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts,
             if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
         }
         if (j == 0) first = best;                       // the largest of all: the softmax's reference point
-        const float p = score == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
+        const float p = score == 2 ? expf(z[best_e] - zmax) / zsum : score == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
         denom += p;
         if (lane == 0) { idx[(size_t)t * top + j] = best_e; wts[(size_t)t * top + j] = p; }
 #pragma unroll
@@ -60,14 +78,18 @@ route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts,
         for (int j = 0; j < top; ++j) wts[(size_t)t * top + j] = wts[(size_t)t * top + j] / denom;
 }
 
-// score 0: the weights are the softmax over the chosen logits; 1: each chosen expert's own sigmoid(logit), not renormalised
+// score 0: the weights are the softmax over the chosen logits; 1: each chosen expert's own sigmoid(logit), not renormalised;
+// 2: each chosen expert's share of the softmax over all experts, not renormalised, the choice going by share + choice_bias
+// (float32 per expert, or null)
 ZI_EXPORT int zi_route_topk(const float* logits, int n_tokens, int n_experts, int top, int* idx, float* wts, int score,
-                            cudaStream_t stream) {
+                            const float* choice_bias, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_experts <= 0 || n_experts > 32 * RT_MAX_PER_LANE) return zi_fail("route_topk: %d experts (1..%d)", n_experts, 32 * RT_MAX_PER_LANE);
     if (top <= 0 || top > n_experts) return zi_fail("route_topk: top=%d of %d experts", top, n_experts);
-    if (score < 0 || score > 1) return zi_fail("route_topk: unknown score rule %d", score);
-    route_topk_kernel<<<(n_tokens + RT_WARPS - 1) / RT_WARPS, RT_WARPS * 32, 0, stream>>>(logits, n_tokens, n_experts, top, idx, wts, score);
+    if (score < 0 || score > 2) return zi_fail("route_topk: unknown score rule %d", score);
+    if (choice_bias && score != 2) return zi_fail("route_topk: a bias on the choice goes with score rule 2 only");
+    route_topk_kernel<<<(n_tokens + RT_WARPS - 1) / RT_WARPS, RT_WARPS * 32, 0, stream>>>(logits, n_tokens, n_experts, top, idx, wts, score,
+                                                                                         choice_bias);
     return zi_check_launch("route_topk");
 }
 
@@ -85,10 +107,11 @@ template <typename TX, typename TW, int RF_TOK>
 __global__ void __launch_bounds__(RF_WARPS * 32)
 route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict__ w, const float* __restrict__ bias,
                    int n_tokens, int K, int n_experts, int top, int* __restrict__ idx, float* __restrict__ wts,
-                   float* __restrict__ logits_out, int score) {
-    extern __shared__ __align__(16) float rf_smem[];              // x rows [RF_TOK][K], then logits [RF_TOK][n_experts]
+                   float* __restrict__ logits_out, int score, const float* __restrict__ choice_bias) {
+    extern __shared__ __align__(16) float rf_smem[];              // x rows [RF_TOK][K], then logits [RF_TOK][n_experts], twice
     float* xs = rf_smem;
     float* z = rf_smem + RF_TOK * K;
+    float* share = z + RF_TOK * n_experts;                        // score rule 2: every expert's share of the softmax over all
     const int t0 = blockIdx.x * RF_TOK, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int toks = n_tokens - t0 < RF_TOK ? n_tokens - t0 : RF_TOK;
     // Rows that are read eight values per lane (vec) lie in two halves: values 8c .. 8c+3 of chunk c at 4c, values
@@ -149,7 +172,21 @@ route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict
     if (warp >= toks) return;                       // warp r chooses for token t0 + r
     const int t = t0 + warp;
     float* zt = z + warp * n_experts;
+    float* st = share + warp * n_experts;
     float first = 0.0f, denom = 0.0f;
+    if (score == 2) {
+        float zmax = -INFINITY, zsum = 0.0f;
+        for (int e = lane; e < n_experts; e += 32) zmax = fmaxf(zmax, zt[e]);
+        zmax = warp_max(zmax);
+        for (int e = lane; e < n_experts; e += 32) zsum += expf(zt[e] - zmax);
+        zsum = warp_sum(zsum);
+        for (int e = lane; e < n_experts; e += 32) {
+            const float p = expf(zt[e] - zmax) / zsum;
+            st[e] = p;
+            zt[e] = p + (choice_bias ? choice_bias[e] : 0.0f);      // what the choice goes by
+        }
+        __syncwarp();
+    }
     for (int j = 0; j < top; ++j) {
         float best = -INFINITY;
         int best_e = 0x7fffffff;
@@ -164,7 +201,7 @@ route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict
             if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
         }
         if (j == 0) first = best;
-        const float p = score == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
+        const float p = score == 2 ? st[best_e] : score == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - first);
         denom += p;
         if (lane == 0) {
             idx[(size_t)t * top + j] = best_e;
@@ -179,13 +216,15 @@ route_fused_kernel(const TX* __restrict__ x, long long ldx, const TW* __restrict
 
 // logits_out: optional float32 [n_tokens, n_experts] (tests).  bias: float32 or null.  score: as zi_route_topk.
 ZI_EXPORT int zi_route(const void* x, int x_dtype, long long ldx, const void* w, int w_dtype, const float* bias, int n_tokens,
-                       int K, int n_experts, int top, int* idx, float* wts, float* logits_out, int score, cudaStream_t stream) {
+                       int K, int n_experts, int top, int* idx, float* wts, float* logits_out, int score, const float* choice_bias,
+                       cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (score < 0 || score > 1) return zi_fail("route: unknown score rule %d", score);
+    if (score < 0 || score > 2) return zi_fail("route: unknown score rule %d", score);
+    if (choice_bias && score != 2) return zi_fail("route: a bias on the choice goes with score rule 2 only");
     if (K <= 0 || n_experts <= 0 || n_experts > 4096) return zi_fail("route: K=%d experts=%d", K, n_experts);
     if (top <= 0 || top > n_experts) return zi_fail("route: top=%d of %d experts", top, n_experts);
     const int tok = n_tokens > 64 ? 4 : 1;
-    const size_t smem = (size_t)tok * ((size_t)K + n_experts) * sizeof(float);
+    const size_t smem = (size_t)tok * ((size_t)K + 2 * (size_t)n_experts) * sizeof(float);
     if (smem > 200 * 1024) return zi_fail("route: a row of %d values and %d logits do not fit shared memory", K, n_experts);
     ZI_DISPATCH(x_dtype, TX, ZI_DISPATCH(w_dtype, TW, {
         auto fn = tok == 4 ? route_fused_kernel<TX, TW, 4> : route_fused_kernel<TX, TW, 1>;
@@ -194,13 +233,14 @@ ZI_EXPORT int zi_route(const void* x, int x_dtype, long long ldx, const void* w,
             if (e != cudaSuccess) return zi_fail("route: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         }
         fn<<<(n_tokens + tok - 1) / tok, RF_WARPS * 32, smem, stream>>>((const TX*)x, ldx, (const TW*)w, bias, n_tokens, K, n_experts, top,
-                                                                        idx, wts, logits_out, score);
+                                                                        idx, wts, logits_out, score, choice_bias);
     }););
     return zi_check_launch("route");
 }
 
 // ---------------------------------------------------------------------------------------
-// Grouping: one block.  offsets[e] .. offsets[e + 1] are the sorted rows of expert e.
+// Grouping: one block.  offsets[e] .. offsets[e + 1] are the sorted rows of expert e.  A pair whose expert is n_experts or
+// more (an expert without weights, which returns its input) gets no sorted row: pair_row is -1 there.
 // ---------------------------------------------------------------------------------------
 #define GROUP_THREADS 1024
 __global__ void __launch_bounds__(GROUP_THREADS)
@@ -211,7 +251,8 @@ moe_group_kernel(const int* __restrict__ idx, int n_pairs, int n_experts, int* _
     int* cursor = sh + n_experts;
     for (int e = threadIdx.x; e < n_experts; e += GROUP_THREADS) counts[e] = 0;
     __syncthreads();
-    for (int p = threadIdx.x; p < n_pairs; p += GROUP_THREADS) atomicAdd(&counts[idx[p]], 1);
+    for (int p = threadIdx.x; p < n_pairs; p += GROUP_THREADS)
+        if (idx[p] < n_experts) atomicAdd(&counts[idx[p]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
@@ -224,6 +265,7 @@ moe_group_kernel(const int* __restrict__ idx, int n_pairs, int n_experts, int* _
     }
     __syncthreads();
     for (int p = threadIdx.x; p < n_pairs; p += GROUP_THREADS) {
+        if (idx[p] >= n_experts) { pair_row[p] = -1; continue; }
         const int r = atomicAdd(&cursor[idx[p]], 1);
         row_pair[r] = p;
         pair_row[p] = r;
@@ -253,7 +295,8 @@ moe_group_padded_kernel(const int* __restrict__ idx, int n_pairs, int n_experts,
     for (int r = threadIdx.x; r < tiles_max * pad; r += GROUP_THREADS) row_pair[r] = -1;
     for (int t = threadIdx.x; t < tiles_max; t += GROUP_THREADS) tile_expert[t] = -1;
     __syncthreads();
-    for (int p = threadIdx.x; p < n_pairs; p += GROUP_THREADS) atomicAdd(&counts[idx[p]], 1);
+    for (int p = threadIdx.x; p < n_pairs; p += GROUP_THREADS)
+        if (idx[p] < n_experts) atomicAdd(&counts[idx[p]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
@@ -268,6 +311,7 @@ moe_group_padded_kernel(const int* __restrict__ idx, int n_pairs, int n_experts,
     }
     __syncthreads();
     for (int p = threadIdx.x; p < n_pairs; p += GROUP_THREADS) {
+        if (idx[p] >= n_experts) { pair_row[p] = -1; continue; }
         const int r = atomicAdd(&cursor[idx[p]], 1);
         row_pair[r] = p;
         pair_row[p] = r;
@@ -756,19 +800,23 @@ ZI_EXPORT int zi_moe_gemm(const void* A, int a_dtype, long long lda, const int* 
 }
 
 // ---------------------------------------------------------------------------------------
-// Combine: out[t, :] = sum_j wts[t, j] * Y[pair_row[t * top + j], :]  (+ shared[t, :]), j rising, float32, one rounding.
+// Combine: out[t, :] = sum_j wts[t, j] * Y[pair_row[t * top + j], :]  (+ shared_gate[t] * shared[t, :]), j rising, float32, one
+// rounding.  A pair without a sorted row (pair_row -1: an expert that returns its input) contributes wts[t, j] * x[t, :].
+// shared_gate null: 1.
 // ---------------------------------------------------------------------------------------
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ Y, const int* __restrict__ pair_row, const float* __restrict__ wts,
-                                   const T* __restrict__ shared, T* __restrict__ out, int top, int hidden) {
+                                   const T* __restrict__ shared, T* __restrict__ out, int top, int hidden,
+                                   const T* __restrict__ x, long long ldx, const float* __restrict__ shared_gate) {
     const int t = blockIdx.x;
     for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
         float acc = 0.0f;
         for (int c = 0; c < top; ++c) {
             const int r = pair_row[(size_t)t * top + c];
-            acc = fmaf(wts ? wts[(size_t)t * top + c] : 1.0f, to_f32<T>(Y[(size_t)r * hidden + j]), acc);
+            const float y = r >= 0 ? to_f32<T>(Y[(size_t)r * hidden + j]) : to_f32<T>(x[(size_t)t * ldx + j]);
+            acc = fmaf(wts ? wts[(size_t)t * top + c] : 1.0f, y, acc);
         }
-        if (shared) acc += to_f32<T>(shared[(size_t)t * hidden + j]);
+        if (shared) acc = fmaf(shared_gate ? shared_gate[t] : 1.0f, to_f32<T>(shared[(size_t)t * hidden + j]), acc);
         out[(size_t)t * hidden + j] = from_f32<T>(acc);
     }
 }
@@ -776,7 +824,8 @@ __global__ void moe_combine_kernel(const T* __restrict__ Y, const int* __restric
 // The same, eight columns per thread with 16- or 32-byte accesses (hidden % 8 == 0, aligned rows); the same sums.
 template <typename T>
 __global__ void moe_combine_vec8_kernel(const T* __restrict__ Y, const int* __restrict__ pair_row, const float* __restrict__ wts,
-                                        const T* __restrict__ shared, T* __restrict__ out, int top, int hidden) {
+                                        const T* __restrict__ shared, T* __restrict__ out, int top, int hidden,
+                                        const T* __restrict__ x, long long ldx, const float* __restrict__ shared_gate) {
     const int t = blockIdx.x;
     for (int j = threadIdx.x * 8; j < hidden; j += blockDim.x * 8) {
         float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
@@ -784,34 +833,36 @@ __global__ void moe_combine_vec8_kernel(const T* __restrict__ Y, const int* __re
             const int r = pair_row[(size_t)t * top + c];
             const float wt = wts ? wts[(size_t)t * top + c] : 1.0f;
             float v[8];
-            load8(Y + (size_t)r * hidden + j, v);
+            load8(r >= 0 ? Y + (size_t)r * hidden + j : x + (size_t)t * ldx + j, v);
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[i] = fmaf(wt, v[i], acc[i]);
         }
         if (shared) {
             float v[8];
             load8(shared + (size_t)t * hidden + j, v);
+            const float g = shared_gate ? shared_gate[t] : 1.0f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] += v[i];
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(g, v[i], acc[i]);
         }
         store8(out + (size_t)t * hidden + j, acc);
     }
 }
 
 ZI_EXPORT int zi_moe_combine(const void* Y, const int* pair_row, const float* wts, const void* shared, void* out, int dtype,
-                             int n_tokens, int top, int hidden, cudaStream_t stream) {
+                             int n_tokens, int top, int hidden, const void* x, long long ldx, const float* shared_gate,
+                             cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (top <= 0 || hidden <= 0) return zi_fail("moe_combine: top=%d hidden=%d", top, hidden);
-    if (hidden % 8 == 0 && (((uintptr_t)Y | (uintptr_t)shared | (uintptr_t)out) & 31) == 0) {
+    if (hidden % 8 == 0 && (((uintptr_t)Y | (uintptr_t)shared | (uintptr_t)out | (uintptr_t)x) & 31) == 0 && ldx % 16 == 0) {
         ZI_DISPATCH(dtype, T, {
             moe_combine_vec8_kernel<T><<<n_tokens, hidden >= 2048 ? 256 : 128, 0, stream>>>((const T*)Y, pair_row, wts, (const T*)shared,
-                                                                                           (T*)out, top, hidden);
+                                                                                           (T*)out, top, hidden, (const T*)x, ldx, shared_gate);
         });
         return zi_check_launch("moe_combine");
     }
     ZI_DISPATCH(dtype, T, {
         moe_combine_kernel<T><<<n_tokens, hidden >= 1024 ? 256 : 128, 0, stream>>>((const T*)Y, pair_row, wts, (const T*)shared,
-                                                                                  (T*)out, top, hidden);
+                                                                                  (T*)out, top, hidden, (const T*)x, ldx, shared_gate);
     });
     return zi_check_launch("moe_combine");
 }

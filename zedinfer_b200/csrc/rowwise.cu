@@ -508,7 +508,7 @@ template <typename T>
 __global__ void __launch_bounds__(RN_WARPS * 32)
 rotary_norm_kernel(const T* __restrict__ x, long long ldx, T* __restrict__ q_out, T* __restrict__ cache, const int* __restrict__ tables,
                    const int* __restrict__ tok_seg, const int* __restrict__ pos, const float* __restrict__ inv_freq, float mag,
-                   int n_q, int n_k, int qk_dim, int v_dim, int row_dim, int rot_dims, int interleaved, int unit_norm, float eps,
+                   const float* __restrict__ q_head_scale, int n_q, int n_k, int qk_dim, int v_dim, int row_dim, int rot_dims, int interleaved, int unit_norm, float eps,
                    int page_size, int max_blocks, long long page_stride, long long kv_stride) {
     extern __shared__ float rn_smem[];       // cos[half], sin[half], then a head per warp
     const int n = blockIdx.x, half = rot_dims >> 1;
@@ -561,13 +561,15 @@ rotary_norm_kernel(const T* __restrict__ x, long long ldx, T* __restrict__ q_out
             ss = warp_sum(ss);
             r = 1.0f / sqrtf(ss / (float)qk_dim + eps);
         }
+        if (q_head_scale && h < n_q) r *= q_head_scale[h];         // a query head's own factor on its scores
         for (int d = lane; d < row_dim; d += 32) dst[d] = from_f32<T>(d < qk_dim ? head[d] * r : 0.0f);
         __syncwarp();
     }
 }
 
 ZI_EXPORT int zi_rotary_norm(const void* x, int dtype, long long ldx, void* q_out, void* cache, const int* tables, const int* tok_seg,
-                             const int* pos, const float* inv_freq, float mag, int n_tokens, int n_q, int n_k, int qk_dim, int v_dim,
+                             const int* pos, const float* inv_freq, float mag, const float* q_head_scale, int n_tokens, int n_q, int n_k,
+                             int qk_dim, int v_dim,
                              int row_dim, int rot_dims, int interleaved, int unit_norm, float eps, int page_size, int max_blocks,
                              long long page_stride, long long kv_stride, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
@@ -582,7 +584,7 @@ ZI_EXPORT int zi_rotary_norm(const void* x, int dtype, long long ldx, void* q_ou
     if (smem > 48 * 1024) return zi_fail("rotary_norm: heads of %d entries are too wide", qk_dim);
     ZI_DISPATCH(dtype, T, {
         rotary_norm_kernel<T><<<n_tokens, RN_WARPS * 32, smem, stream>>>((const T*)x, ldx, (T*)q_out, (T*)cache, tables, tok_seg, pos,
-                                                                         inv_freq, mag, n_q, n_k, qk_dim, v_dim, row_dim, rot_dims,
+                                                                         inv_freq, mag, q_head_scale, n_q, n_k, qk_dim, v_dim, row_dim, rot_dims,
                                                                          interleaved, unit_norm, eps, page_size, max_blocks, page_stride,
                                                                          kv_stride);
     });
@@ -697,4 +699,199 @@ ZI_EXPORT int zi_gelu_mul_rows(const void* t, int dtype, long long ldt, const vo
                                                                                                  col0, ids, vocab, (T*)out, width, total);
     }););
     return zi_check_launch("gelu_mul_rows");
+}
+
+// ---------------------------------------------------------------------------------------
+// The tanh norm  N(v; a, w, b) = tanh(a v) * w + b  (a scalar a, vectors w and b; no mean, no variance) around the float32
+// residual stream, for layers with a norm before and a norm after every sublayer:
+//     v = h[row] + N(y[row]; post)        where a branch's output y is pending (y null: v = h[row])
+//     h[row] = v                          where write_h is set
+//     out[r] = N(v; pre)                  where out is given
+// row = row_idx[r] where row_idx is given (then h is not written), else r.  h float32; y and out of the step's type; w, b
+// float32.  Entry by entry, so a row's result depends on nothing else.
+// ---------------------------------------------------------------------------------------
+struct TanhNormArgs { float a; const float* w; const float* b; };
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+tanh_norm_fold_kernel(float* __restrict__ h, const T* __restrict__ y, TanhNormArgs post, TanhNormArgs pre, T* __restrict__ out,
+                      const int* __restrict__ row_idx, int write_h, int hidden) {
+    const size_t r = blockIdx.x, row = row_idx ? (size_t)row_idx[r] : r;
+    float* hr = h + row * hidden;
+    const T* yr = y ? y + row * hidden : nullptr;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        float v = hr[j];
+        if (yr) v += tanhf(post.a * to_f32<T>(yr[j])) * post.w[j] + post.b[j];
+        if (write_h) hr[j] = v;
+        if (out) out[r * hidden + j] = from_f32<T>(tanhf(pre.a * v) * pre.w[j] + pre.b[j]);
+    }
+}
+
+// The same with eight entries per access; hidden a multiple of 8 and every pointer on a 32-byte boundary.
+template <typename T>
+__global__ void __launch_bounds__(256)
+tanh_norm_fold_vec8_kernel(float* __restrict__ h, const T* __restrict__ y, TanhNormArgs post, TanhNormArgs pre, T* __restrict__ out,
+                           const int* __restrict__ row_idx, int write_h, int hidden) {
+    const size_t r = blockIdx.x, row = row_idx ? (size_t)row_idx[r] : r;
+    float* hr = h + row * hidden;
+    const T* yr = y ? y + row * hidden : nullptr;
+    for (int j = threadIdx.x * 8; j < hidden; j += blockDim.x * 8) {
+        float v[8];
+        load8(hr + j, v);
+        if (yr) {
+            float t[8], w[8], b[8];
+            load8(yr + j, t); load8(post.w + j, w); load8(post.b + j, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] += tanhf(post.a * t[e]) * w[e] + b[e];
+        }
+        if (write_h) store8(hr + j, v);
+        if (out) {
+            float w[8], b[8], o[8];
+            load8(pre.w + j, w); load8(pre.b + j, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = tanhf(pre.a * v[e]) * w[e] + b[e];
+            store8(out + r * hidden + j, o);
+        }
+    }
+}
+
+ZI_EXPORT int zi_tanh_norm_fold(float* h, const void* y, int dtype, float post_a, const float* post_w, const float* post_b, float pre_a,
+                                const float* pre_w, const float* pre_b, void* out, const int* row_idx, int rows, int hidden, int write_h,
+                                cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0) return zi_fail("tanh_norm_fold: hidden=%d", hidden);
+    if (y && (!post_w || !post_b)) return zi_fail("tanh_norm_fold: a pending branch needs the norm that follows it");
+    if (out && (!pre_w || !pre_b)) return zi_fail("tanh_norm_fold: an output needs the norm that makes it");
+    if (row_idx && write_h) return zi_fail("tanh_norm_fold: chosen rows leave the stream as it is");
+    const TanhNormArgs post{post_a, post_w, post_b}, pre{pre_a, pre_w, pre_b};
+    const int threads = hidden >= 2048 ? 256 : 128;
+    // which form runs depends on the sizes and on where the buffers start, never on the rows of the step
+    const bool vec = hidden % 8 == 0 && (((size_t)h | (size_t)y | (size_t)out | (size_t)post_w | (size_t)post_b | (size_t)pre_w | (size_t)pre_b) & 31) == 0;
+    ZI_DISPATCH(dtype, T, {
+        if (vec) tanh_norm_fold_vec8_kernel<T><<<rows, threads, 0, stream>>>(h, (const T*)y, post, pre, (T*)out, row_idx, write_h, hidden);
+        else tanh_norm_fold_kernel<T><<<rows, threads, 0, stream>>>(h, (const T*)y, post, pre, (T*)out, row_idx, write_h, hidden);
+    });
+    return zi_check_launch("tanh_norm_fold");
+}
+
+// out = tanh(a x) * w + b for rows of any of the two types (a norm called on its own).
+template <typename TX, typename T>
+__global__ void tanh_norm_kernel(const TX* __restrict__ x, TanhNormArgs nm, T* __restrict__ out, int hidden, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int j = (int)(i % hidden);
+        out[i] = from_f32<T>(tanhf(nm.a * to_f32<TX>(x[i])) * nm.w[j] + nm.b[j]);
+    }
+}
+
+ZI_EXPORT int zi_tanh_norm(const void* x, int x_dtype, float a, const float* w, const float* b, void* out, int dtype, int rows, int hidden,
+                           cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || !w || !b) return zi_fail("tanh_norm: hidden=%d, weight and bias are needed", hidden);
+    const size_t total = (size_t)rows * hidden, want = (total + 255) / 256;
+    const TanhNormArgs nm{a, w, b};
+    ZI_DISPATCH(x_dtype, TX, ZI_DISPATCH(dtype, T, {
+        tanh_norm_kernel<TX, T><<<(int)(want > 148 * 16 ? 148 * 16 : want), 256, 0, stream>>>((const TX*)x, nm, (T*)out, hidden, total);
+    }););
+    return zi_check_launch("tanh_norm");
+}
+
+// ---------------------------------------------------------------------------------------
+// Two branches that read the same input, joined:  out = (U(x) * wx + U(z) * wz) / 2  with U(v) = v / sqrt(mean(v^2) + eps)
+// over a row, float32 inside; wx, wz float32.  One block per row.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_pair_mean_kernel(const T* __restrict__ x, const T* __restrict__ z, const float* __restrict__ wx, const float* __restrict__ wz,
+                     T* __restrict__ out, float eps, int hidden) {
+    extern __shared__ float pm_row[];                    // x's row, then z's
+    __shared__ float scratch[32];
+    const size_t n = blockIdx.x;
+    float sx = 0.0f, sz = 0.0f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        const float a = to_f32<T>(x[n * hidden + j]), b = to_f32<T>(z[n * hidden + j]);
+        pm_row[j] = a; pm_row[hidden + j] = b;
+        sx = fmaf(a, a, sx); sz = fmaf(b, b, sz);
+    }
+    sx = block_sum(sx, scratch);
+    sz = block_sum(sz, scratch);
+    const float rx = 1.0f / sqrtf(sx / (float)hidden + eps), rz = 1.0f / sqrtf(sz / (float)hidden + eps);
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x)
+        out[n * hidden + j] = from_f32<T>(0.5f * ((pm_row[j] * rx) * wx[j] + (pm_row[hidden + j] * rz) * wz[j]));
+}
+
+ZI_EXPORT int zi_rms_pair_mean(const void* x, const void* z, int dtype, const float* wx, const float* wz, void* out, float eps, int rows,
+                               int hidden, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || (size_t)hidden * 2 * sizeof(float) > 48 * 1024) return zi_fail("rms_pair_mean: hidden=%d is not supported", hidden);
+    ZI_DISPATCH(dtype, T, {
+        rms_pair_mean_kernel<T><<<rows, hidden >= 2048 ? 256 : 128, (size_t)hidden * 2 * sizeof(float), stream>>>(
+            (const T*)x, (const T*)z, wx, wz, (T*)out, eps, hidden);
+    });
+    return zi_check_launch("rms_pair_mean");
+}
+
+// ---------------------------------------------------------------------------------------
+// A feed-forward activation from powers of its input, each divided by its own root mean square over the row:
+//     out = c1 U(z) + c2 U(z^2) + c3 U(z^3) + c0,   U(v) = v / sqrt(mean(v^2) + eps),  powers entry by entry
+// float32 inside.  One block per row; rows of z may be strided.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+poly_norm_kernel(const T* __restrict__ z, long long ldz, T* __restrict__ out, int width, float c1, float c2, float c3, float c0, float eps) {
+    extern __shared__ float pn_row[];
+    __shared__ float scratch[32];
+    const size_t n = blockIdx.x;
+    float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float v = to_f32<T>(z[n * ldz + j]), v2 = v * v, v3 = v2 * v;
+        pn_row[j] = v;
+        s2 += v2; s4 = fmaf(v2, v2, s4); s6 = fmaf(v3, v3, s6);
+    }
+    s2 = block_sum(s2, scratch);
+    s4 = block_sum(s4, scratch);
+    s6 = block_sum(s6, scratch);
+    const float r1 = 1.0f / sqrtf(s2 / (float)width + eps), r2 = 1.0f / sqrtf(s4 / (float)width + eps), r3 = 1.0f / sqrtf(s6 / (float)width + eps);
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        const float v = pn_row[j], v2 = v * v, v3 = v2 * v;
+        out[n * width + j] = from_f32<T>(c1 * (v * r1) + c2 * (v2 * r2) + c3 * (v3 * r3) + c0);
+    }
+}
+
+ZI_EXPORT int zi_poly_norm(const void* z, int dtype, long long ldz, void* out, int rows, int width, float c1, float c2, float c3, float c0,
+                           float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (width <= 0 || smem > 200 * 1024) return zi_fail("poly_norm: width=%d is not supported", width);
+    ZI_DISPATCH(dtype, T, {
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(poly_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return zi_fail("poly_norm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+        }
+        poly_norm_kernel<T><<<rows, 256, smem, stream>>>((const T*)z, ldz, (T*)out, width, c1, c2, c3, c0, eps);
+    });
+    return zi_check_launch("poly_norm");
+}
+
+// ---------------------------------------------------------------------------------------
+// One gate per row:  g[n] = sigmoid(x[n, :] . w)  in float32 (x, w of any of the two types).  One block per row, the lanes'
+// sums in a fixed order.
+// ---------------------------------------------------------------------------------------
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128)
+row_gate_kernel(const T* __restrict__ x, long long ldx, const TW* __restrict__ w, float* __restrict__ g, int K) {
+    __shared__ float scratch[32];
+    const size_t n = blockIdx.x;
+    float acc = 0.0f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) acc = fmaf(to_f32<T>(x[n * ldx + k]), to_f32<TW>(w[k]), acc);
+    acc = block_sum(acc, scratch);
+    if (threadIdx.x == 0) g[n] = 1.0f / (1.0f + expf(-acc));
+}
+
+ZI_EXPORT int zi_row_gate(const void* x, int dtype, long long ldx, const void* w, int w_dtype, float* g, int rows, int K, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (K <= 0) return zi_fail("row_gate: K=%d", K);
+    ZI_DISPATCH(dtype, T, ZI_DISPATCH(w_dtype, TW, {
+        row_gate_kernel<T, TW><<<rows, 128, 0, stream>>>((const T*)x, ldx, (const TW*)w, g, K);
+    }););
+    return zi_check_launch("row_gate");
 }

@@ -38,7 +38,8 @@ __all__ = ["KernelError", "embedding", "rmsnorm", "add_rmsnorm", "rope_append", 
            "moe_group", "moe_gemm", "moe_combine", "linear_gated_clamp_mul", "linear_relu2", "moe_group_padded",
            "moe_gather_rows", "gemm_tcgen05_grouped", "route", "rotary", "latent_prepare", "sigmoid_mul", "segment_bounds",
            "causal_conv_silu", "conv_state_update", "ssm_scan", "gated_group_rmsnorm", "rotary_norm", "norm_add", "gelu_mul_rows",
-           "linear_state", "linear_state_work_floats", "group_rmsnorm_gate"]
+           "linear_state", "linear_state_work_floats", "group_rmsnorm_gate", "tanh_norm", "tanh_norm_fold", "rms_pair_mean", "poly_norm",
+           "row_gate"]
 
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
@@ -926,28 +927,42 @@ def linear_per_head(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None
 
 
 # ---- routed feed-forward, csrc/moe.cu ------------------------------------------------------------------------------
-ROUTER_SCORES = {"softmax_chosen": 0, "sigmoid": 1}
+ROUTER_SCORES = {"softmax_chosen": 0, "sigmoid": 1, "softmax_all": 2}
 
 
-def route_topk(logits: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor, score: str = "softmax_chosen") -> None:
+def _check_choice_bias(choice_bias: Optional[torch.Tensor], experts: int, score: str) -> None:
+    if choice_bias is not None and (score != "softmax_all" or choice_bias.dtype != torch.float32 or choice_bias.numel() != experts
+                                    or not choice_bias.is_contiguous()):
+        raise KernelError(f"route: choice_bias must be contiguous float32 with {experts} entries and goes with score='softmax_all'")
+
+
+def route_topk(logits: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor, score: str = "softmax_chosen",
+               choice_bias: Optional[torch.Tensor] = None) -> None:
     """Per row of float32 ``logits [tokens, experts]``: the ``top`` largest (lowest index wins a tie) into ``idx`` (int32
     ``[tokens, top]``, largest first) and their weights into ``wts`` (float32): the softmax over those alone
-    (``score="softmax_chosen"``), or each one's own ``sigmoid(logit)``, not renormalised (``"sigmoid"``)."""
-    need_cuda(logits, idx, wts)
+    (``score="softmax_chosen"``), or each one's own ``sigmoid(logit)``, not renormalised (``"sigmoid"``).
+    ``score="softmax_all"``: every expert's score is its share of the softmax over all experts; the ``top`` largest of
+    ``score + choice_bias`` are chosen (``choice_bias`` float32 per expert, or None) and their weights are the scores
+    themselves, without the bias and not renormalised."""
+    need_cuda(logits, idx, wts, choice_bias)
+    _check_choice_bias(choice_bias, logits.shape[1], score)
     need_int32("idx", idx)
     need_contiguous("logits", logits), need_contiguous("idx", idx), need_contiguous("wts", wts)
     n, e = logits.shape
     if logits.dtype != torch.float32 or wts.dtype != torch.float32 or idx.shape != (n, top) or wts.shape != (n, top):
         raise KernelError(f"route_topk: logits {tuple(logits.shape)} {logits.dtype}, idx {tuple(idx.shape)}, wts {tuple(wts.shape)}")
-    _moe.call("zi_route_topk", ptr(logits), c_int(n), c_int(e), c_int(top), ptr(idx), ptr(wts), c_int(ROUTER_SCORES[score]), stream())
+    _moe.call("zi_route_topk", ptr(logits), c_int(n), c_int(e), c_int(top), ptr(idx), ptr(wts), c_int(ROUTER_SCORES[score]),
+              ptr(choice_bias), stream())
 
 
 def route(x: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor,
-          wts: torch.Tensor, logits: Optional[torch.Tensor] = None, score: str = "softmax_chosen") -> None:
+          wts: torch.Tensor, logits: Optional[torch.Tensor] = None, score: str = "softmax_chosen",
+          choice_bias: Optional[torch.Tensor] = None) -> None:
     """The router in one kernel: float32 logits ``x @ w_router.T + bias`` (operands of any storage type, float32 sums in
-    a fixed order), then as :func:`route_topk` (``score`` as there).  ``logits``: optional float32 ``[tokens, experts]`` to
-    receive them."""
-    need_cuda(x, w_router, bias, idx, wts, logits)
+    a fixed order), then as :func:`route_topk` (``score`` and ``choice_bias`` as there).  ``logits``: optional float32
+    ``[tokens, experts]`` to receive them."""
+    need_cuda(x, w_router, bias, idx, wts, logits, choice_bias)
+    _check_choice_bias(choice_bias, w_router.shape[0], score)
     need_int32("idx", idx)
     need_contiguous("w_router", w_router), need_contiguous("idx", idx), need_contiguous("wts", wts)
     n, k = x.shape
@@ -958,7 +973,7 @@ def route(x: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor],
         raise KernelError(f"route: x {tuple(x.shape)}, w_router {tuple(w_router.shape)}, idx {tuple(idx.shape)}, wts {tuple(wts.shape)}")
     _moe.call("zi_route", ptr(x), c_int(dtype_code(x.dtype)), c_ll(x.stride(0)), ptr(w_router), c_int(dtype_code(w_router.dtype)),
               ptr(bias), c_int(n), c_int(k), c_int(e), c_int(top), ptr(idx), ptr(wts), ptr(logits), c_int(ROUTER_SCORES[score]),
-              stream())
+              ptr(choice_bias), stream())
 
 
 def moe_group(idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, row_pair: torch.Tensor, pair_row: torch.Tensor) -> None:
@@ -1070,11 +1085,16 @@ def moe_gemm(a: torch.Tensor, row_pair: Optional[torch.Tensor], pairs_per_src: i
 
 
 def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, wts: Optional[torch.Tensor], shared: Optional[torch.Tensor],
-                out: torch.Tensor) -> None:
-    """``out[t] = sum_j wts[t, j] * y[pair_row[t, j]] (+ shared[t])``, j rising, in float32 with one rounding.  ``y`` has
-    a row per pair, or more where the sorted rows are padded.  ``wts`` None: every weight is 1 (``pair_row`` is then
-    ``[tokens, top]``)."""
-    need_cuda(y, pair_row, wts, shared, out)
+                out: torch.Tensor, x: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None) -> None:
+    """``out[t] = sum_j wts[t, j] * y[pair_row[t, j]] (+ shared_gate[t] * shared[t])``, j rising, in float32 with one rounding.
+    ``y`` has a row per pair, or more where the sorted rows are padded.  ``wts`` None: every weight is 1 (``pair_row`` is then
+    ``[tokens, top]``).  ``x``: the tokens' inputs; a pair whose ``pair_row`` is -1 (an expert that returns its input, see
+    :func:`moe_group`) contributes ``wts[t, j] * x[t]``.  ``shared_gate``: float32, one factor per token (None: 1)."""
+    need_cuda(y, pair_row, wts, shared, out, x, shared_gate)
+    if x is not None and (x.shape != out.shape or x.dtype != out.dtype or x.stride(1) != 1):
+        raise KernelError(f"moe_combine: x {tuple(x.shape)} must have out's shape and type")
+    if shared_gate is not None and (shared_gate.dtype != torch.float32 or shared_gate.numel() != out.shape[0] or not shared_gate.is_contiguous()):
+        raise KernelError("moe_combine: shared_gate must be contiguous float32 with one entry per token")
     need_int32("pair_row", pair_row)
     need_contiguous("y", y), need_contiguous("pair_row", pair_row), need_contiguous("out", out)
     n, hidden = out.shape
@@ -1088,7 +1108,7 @@ def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, wts: Optional[torch.Ten
                                                                 or not shared.is_contiguous())):
         raise KernelError(f"moe_combine: y {tuple(y.shape)}, {n} x {top} weights, out {tuple(out.shape)} do not agree")
     _moe.call("zi_moe_combine", ptr(y), ptr(pair_row), ptr(wts), ptr(shared), ptr(out), c_int(dtype_code(out.dtype)), c_int(n),
-              c_int(top), c_int(hidden), stream())
+              c_int(top), c_int(hidden), ptr(x), c_ll(x.stride(0) if x is not None else 0), ptr(shared_gate), stream())
 
 
 # ---- rotation of a span of every head, latents with a rotated key part, output gate: csrc/rowwise.cu ------------------------
@@ -1265,14 +1285,18 @@ def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, n_gro
 # ---- a gate on a token's own table entry: csrc/rowwise.cu -------------------------------------------------------------------
 def rotary_norm(x: torch.Tensor, q_out: torch.Tensor, pos: torch.Tensor, inv_freq: Optional[torch.Tensor], mag: float, n_q: int,
                 n_k: int, qk_dim: int, v_dim: int, row_dim: int, rot_dims: int, interleaved: bool, unit_eps: Optional[float],
-                cache=None, tables: Optional[torch.Tensor] = None, tok_seg: Optional[torch.Tensor] = None) -> None:
+                cache=None, tables: Optional[torch.Tensor] = None, tok_seg: Optional[torch.Tensor] = None,
+                q_head_scale: Optional[torch.Tensor] = None) -> None:
     """Turn the first ``rot_dims`` entries of every query and key head of ``x`` (``[tokens, (n_q + n_k) * qk_dim + n_k *
     v_dim]``, rows may be strided) by the token's position (pairing and angles as :func:`rotary`; cosines and sines times
     ``mag``), then, with ``unit_eps``, divide every query and key head by its root mean square ``sqrt(mean + unit_eps)``.
     Queries go to ``q_out`` (``[tokens, n_q, row_dim]``), keys and values to the two planes of ``cache`` (a CallCacheView whose
     rows are ``row_dim`` wide); what lies past a head's own entries is written as zero.  ``cache`` None: queries alone (``x``
-    then holds no keys and values)."""
-    need_cuda(x, q_out, pos, inv_freq, tables, tok_seg)
+    then holds no keys and values).  ``q_head_scale`` (float32, one per query head): every query head is multiplied by its
+    own factor as it is written, which multiplies that head's scores."""
+    need_cuda(x, q_out, pos, inv_freq, tables, tok_seg, q_head_scale)
+    if q_head_scale is not None and (q_head_scale.dtype != torch.float32 or q_head_scale.numel() != n_q or not q_head_scale.is_contiguous()):
+        raise KernelError(f"rotary_norm: q_head_scale must be contiguous float32 with {n_q} entries")
     need_int32("pos", pos)
     need_contiguous("q_out", q_out)
     n = x.shape[0]
@@ -1289,7 +1313,7 @@ def rotary_norm(x: torch.Tensor, q_out: torch.Tensor, pos: torch.Tensor, inv_fre
         if x.shape[1] < (n_q + n_k) * qk_dim + n_k * v_dim:
             raise KernelError("rotary_norm: x is too narrow for its heads")
     _rowwise.call("zi_rotary_norm", ptr(x), c_int(dtype_code(x.dtype)), c_ll(x.stride(0)), ptr(q_out), ptr(ct), ptr(tables), ptr(tok_seg),
-                  ptr(pos), ptr(inv_freq), c_float(mag), c_int(n), c_int(n_q), c_int(n_k if cache is not None else 0), c_int(qk_dim),
+                  ptr(pos), ptr(inv_freq), c_float(mag), ptr(q_head_scale), c_int(n), c_int(n_q), c_int(n_k if cache is not None else 0), c_int(qk_dim),
                   c_int(v_dim), c_int(row_dim), c_int(rot_dims), c_int(1 if interleaved else 0), c_int(1 if unit_eps is not None else 0),
                   c_float(unit_eps or 0.0), c_int(cache.page_size if cache is not None else 0),
                   c_int(tables.shape[1] if tables is not None else 0), c_ll(cache.page_stride if cache is not None else 0),
@@ -1322,21 +1346,27 @@ def gelu_mul_rows(t: torch.Tensor, table: torch.Tensor, col0: int, ids: torch.Te
 
 
 # ---- linear recurrences with a matrix state per head, csrc/linrec.cu ---------------------------------------------------------
-LINEAR_STATE_RULES = {"delta": 0, "decay": 1}
+LINEAR_STATE_RULES = {"delta": 0, "decay": 1, "forget": 2}
+_SILU_ON = {"q": 1, "k": 2, "v": 4}
 
 
 def linear_state(rule: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, slots: torch.Tensor,
                  bounds: Optional[torch.Tensor], y: torch.Tensor, n_segments: int, heads: int, kv_heads: int, dim: int, vdim: int,
                  a: Optional[torch.Tensor] = None, b: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None,
-                 a_log: Optional[torch.Tensor] = None, decay: Optional[torch.Tensor] = None, act_silu: bool = False,
-                 q_scale: float = 1.0, unit_eps: float = 1e-6, work: Optional[torch.Tensor] = None) -> None:
+                 a_log: Optional[torch.Tensor] = None, decay: Optional[torch.Tensor] = None, act_silu=False,
+                 q_scale: float = 1.0, unit_eps: float = 1e-6, work: Optional[torch.Tensor] = None,
+                 decay_per_head: bool = False) -> None:
     """Walk each segment's tokens in order through a float32 state ``S`` (``dim x vdim``) per head.
 
     ``rule="delta"``: ``S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` with ``q`` and ``k`` made unit vectors
     per head (``x / sqrt(sum x^2 + unit_eps)``; ``q`` also times ``q_scale``), ``beta = sigmoid(b)`` (``b [tokens, heads]``) and
     ``g = exp(-exp(a_log) softplus(a + dt_bias))`` (``a [tokens, heads * dim]``, ``dt_bias`` float32 ``[heads * dim]``, ``a_log``
-    float32 ``[heads]``).  ``rule="decay"``: ``S <- decay_h S + k v^T; o = S^T q`` (``decay`` float32 ``[heads]``; ``q`` times
-    ``q_scale``).  ``act_silu``: q, k and v pass through SiLU first.  ``q``, ``k`` ``[tokens, kv_heads * dim]`` (head h reads
+    float32 ``[heads]``; with ``decay_per_head`` one decay per head: ``a [tokens, heads]``, ``dt_bias [heads]``).
+    ``rule="decay"``: ``S <- decay_h S + k v^T; o = S^T q`` (``decay`` float32 ``[heads]``; ``q`` times ``q_scale``).
+    ``rule="forget"``: ``S <- diag(f) S + (1 - f) v^T; o = S^T q`` with ``f = l + (1 - l) sigmoid(a)`` per head and key entry
+    (``a [tokens, heads * dim]``, the lower bounds ``l`` in ``dt_bias`` float32 ``[heads * dim]``; ``k`` is None, ``kv_heads``
+    equals ``heads``; ``q`` times ``q_scale``).  ``act_silu``: True: q, k and v pass through SiLU first; a string names which
+    of them do (``"q"``, ``"qk"``, ...).  ``q``, ``k`` ``[tokens, kv_heads * dim]`` (head h reads
     query/key head ``h // (heads / kv_heads)``) and ``v [tokens, heads * vdim]`` may have strided rows; ``y`` float32
     ``[tokens, heads * vdim]``.  A request's state (``[heads, vdim, dim]``, the first entries of its slot of ``state``) is read
     at the start and written back at the end; slot -1: zero, not written.  ``bounds`` from :func:`segment_bounds`; None:
@@ -1346,6 +1376,12 @@ def linear_state(rule: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
     there (all tokens and heads at once) and the walk only copies and walks, which pays for segments of many tokens; without
     it the walk makes its inputs ready itself.  A token's result has the same bits either way."""
     need_cuda(q, k, v, state, slots, bounds, y, a, b, dt_bias, a_log, decay, work)
+    forget = rule == "forget"
+    if forget:
+        if k is not None or kv_heads != heads:
+            raise KernelError("linear_state: the forget rule has no keys and a query head per head")
+        k = q
+    silu_bits = 7 if act_silu is True else sum(_SILU_ON[c] for c in set(act_silu)) if act_silu else 0
     if work is not None and (work.dtype != torch.float32 or not work.is_contiguous()):
         raise KernelError("linear_state: the workspace must be contiguous float32")
     need_int32("slots", slots)
@@ -1355,10 +1391,11 @@ def linear_state(rule: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
             or v.shape != (n, heads * vdim) or not (q.dtype == k.dtype == v.dtype) or y.dtype != torch.float32
             or y.shape != (n, heads * vdim)):
         raise KernelError(f"linear_state: q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}, y {tuple(y.shape)} do not agree")
-    for name, t, width in (("a", a, heads * dim), ("b", b, heads)):
+    per_head = bool(decay_per_head) and rule == "delta"
+    for name, t, width in (("a", a, heads if per_head else heads * dim), ("b", b, heads)):
         if t is not None and (t.shape != (n, width) or t.stride(1) != 1 or t.dtype != q.dtype):
             raise KernelError(f"linear_state: {name} must be [tokens, {width}] of q's type")
-    for name, t, count in (("dt_bias", dt_bias, heads * dim), ("a_log", a_log, heads), ("decay", decay, heads)):
+    for name, t, count in (("dt_bias", dt_bias, heads if per_head else heads * dim), ("a_log", a_log, heads), ("decay", decay, heads)):
         if t is not None and (t.dtype != torch.float32 or t.numel() != count or not t.is_contiguous()):
             raise KernelError(f"linear_state: {name} must be contiguous float32 with {count} entries")
     if state.shape[1] < heads * vdim * dim:
@@ -1367,7 +1404,7 @@ def linear_state(rule: str, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, s
     _linrec.call("zi_linear_state", c_int(LINEAR_STATE_RULES[rule]), ptr(q), c_ll(q.stride(0)), ptr(k), c_ll(k.stride(0)), ptr(v),
                  c_ll(v.stride(0)), ptr(a), c_ll(a.stride(0) if a is not None else 0), ptr(b), c_ll(b.stride(0) if b is not None else 0),
                  c_int(dtype_code(q.dtype)), ptr(dt_bias), ptr(a_log), ptr(decay), sp, ss, ptr(slots), ptr(bounds), ptr(y), c_int(n),
-                 c_int(n_segments), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(1 if act_silu else 0),
+                 c_int(n_segments), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_int(silu_bits), c_int(1 if per_head else 0),
                  c_float(q_scale), c_float(unit_eps), ptr(work), c_ll(work.numel() if work is not None else 0), stream())
 
 
@@ -1376,17 +1413,112 @@ def linear_state_work_floats(rule: str, n_tokens: int, heads: int, dim: int, vdi
     and head a record of q, k (and the decays in the delta rule) padded to the kernel's 32, 64, 128 or 256 entries plus
     four scalars, and the values padded to whole tiles of 16 columns."""
     padded = 32 if dim <= 32 else 64 if dim <= 64 else 128 if dim <= 128 else 256
-    record = (3 if LINEAR_STATE_RULES[rule] == 0 else 2) * padded + 4
+    record = (2 if rule == "decay" else 3) * padded + 4
     return n_tokens * heads * (record + (vdim + 15) // 16 * 16)
 
 
-def group_rmsnorm_gate(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, n_groups: int, eps: float, out: torch.Tensor) -> None:
-    """``out = unit_rms(y) * w * sigmoid(z)`` with the root mean square over each of ``n_groups`` equal parts of a row and
-    ``w`` repeated along the row when it is shorter; ``y`` float32, ``z`` (rows may be strided) and ``out`` of the step's type."""
+GROUP_NORM_GATES = {"sigmoid": 0, "silu": 1, None: 2}
+
+
+def group_rmsnorm_gate(y: torch.Tensor, z: Optional[torch.Tensor], w: torch.Tensor, n_groups: int, eps: float, out: torch.Tensor,
+                       gate: Optional[str] = "sigmoid") -> None:
+    """``out = unit_rms(y) * w * gate(z)`` with the root mean square over each of ``n_groups`` equal parts of a row and
+    ``w`` repeated along the row when it is shorter; ``y`` float32, ``z`` (rows may be strided) and ``out`` of the step's type.
+    ``gate``: ``"sigmoid"``, ``"silu"`` or None (no gate; ``z`` is then None)."""
     need_cuda(y, z, w, out)
     need_contiguous("y", y), need_contiguous("w", w), need_contiguous("out", out)
     n, inner = y.shape
-    if y.dtype != torch.float32 or z.shape != (n, inner) or z.stride(1) != 1 or out.shape != (n, inner) or out.dtype != z.dtype:
-        raise KernelError(f"group_rmsnorm_gate: y {tuple(y.shape)}, z {tuple(z.shape)}, out {tuple(out.shape)} do not agree")
-    _linrec.call("zi_group_rmsnorm_gate", ptr(y), ptr(z), c_int(dtype_code(z.dtype)), c_ll(z.stride(0)), ptr(w), c_int(dtype_code(w.dtype)),
-                 c_int(w.numel()), ptr(out), c_int(n), c_int(inner), c_int(n_groups), c_float(eps), stream())
+    if gate not in GROUP_NORM_GATES or (gate is None) != (z is None):
+        raise KernelError(f"group_rmsnorm_gate: gate={gate!r} is not 'sigmoid', 'silu' or None, or does not fit z")
+    if y.dtype != torch.float32 or out.shape != (n, inner) or (z is not None and (z.shape != (n, inner) or z.stride(1) != 1 or out.dtype != z.dtype)):
+        raise KernelError(f"group_rmsnorm_gate: y {tuple(y.shape)}, z {tuple(z.shape) if z is not None else None}, out {tuple(out.shape)} do not agree")
+    _linrec.call("zi_group_rmsnorm_gate", ptr(y), ptr(z), c_int(dtype_code(out.dtype)), c_ll(z.stride(0) if z is not None else 0), ptr(w),
+                 c_int(dtype_code(w.dtype)), c_int(w.numel()), ptr(out), c_int(n), c_int(inner), c_int(n_groups), c_float(eps),
+                 c_int(GROUP_NORM_GATES[gate]), stream())
+
+
+# ---- the tanh norm, joined branches, an activation of normed powers, a gate per row: csrc/rowwise.cu -----------------------------
+def _tanh_norm_args(name: str, norm, hidden: int):
+    """``norm``: (alpha, weight, bias) with float32 vectors of ``hidden`` entries, or None."""
+    if norm is None:
+        return c_float(0.0), ptr(None), ptr(None)
+    alpha, w, b = norm
+    for t in (w, b):
+        if t.dtype != torch.float32 or t.numel() != hidden or not t.is_contiguous() or not t.is_cuda:
+            raise KernelError(f"{name}: weight and bias must be contiguous float32 on the device with {hidden} entries")
+    return c_float(float(alpha)), ptr(w), ptr(b)
+
+
+def tanh_norm(x: torch.Tensor, alpha: float, w: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = tanh(alpha x) * w + b`` row by row (float32 inside; ``w``, ``b`` float32)."""
+    need_cuda(x, w, b, out)
+    need_contiguous("x", x), need_contiguous("out", out)
+    rows, hidden = x.shape
+    if out.shape != x.shape:
+        raise KernelError(f"tanh_norm: x {tuple(x.shape)} and out {tuple(out.shape)} do not agree")
+    a, pw, pb = _tanh_norm_args("tanh_norm", (alpha, w, b), hidden)
+    _rowwise.call("zi_tanh_norm", ptr(x), c_int(dtype_code(x.dtype)), a, pw, pb, ptr(out), c_int(dtype_code(out.dtype)), c_int(rows),
+                  c_int(hidden), stream())
+
+
+def tanh_norm_fold(h: torch.Tensor, y: Optional[torch.Tensor], post, pre, out: Optional[torch.Tensor],
+                   row_idx: Optional[torch.Tensor] = None, write_h: bool = True, dtype: Optional[torch.dtype] = None) -> None:
+    """The tanh norm ``N(v; alpha, w, b) = tanh(alpha v) * w + b`` on both sides of the float32 stream ``h``: ``v = h + N(y;
+    post)`` where a branch's output ``y`` is pending (``y`` None: ``v = h``), ``h = v`` where ``write_h``, ``out = N(v; pre)``
+    where ``out`` is given.  ``post``, ``pre``: (alpha, float32 weight, float32 bias) or None.  With ``row_idx`` output row r
+    comes from row ``row_idx[r]`` and ``h`` is left as it is."""
+    need_cuda(h, y, out, row_idx)
+    need_contiguous("h", h)
+    if h.dtype != torch.float32 or h.dim() != 2:
+        raise KernelError(f"tanh_norm_fold: the stream must be float32 [rows, hidden], got {tuple(h.shape)} {h.dtype}")
+    hidden = h.shape[1]
+    if row_idx is not None:
+        need_int32("row_idx", row_idx), need_contiguous("row_idx", row_idx)
+        write_h = False
+    rows = row_idx.numel() if row_idx is not None else h.shape[0]
+    if y is not None and (y.shape != h.shape or not y.is_contiguous() or post is None):
+        raise KernelError("tanh_norm_fold: a pending branch must be contiguous, of h's shape, and bring the norm that follows it")
+    if out is not None and (out.shape != (rows, hidden) or not out.is_contiguous() or pre is None or (y is not None and y.dtype != out.dtype)):
+        raise KernelError(f"tanh_norm_fold: out {tuple(out.shape)} does not fit {(rows, hidden)}, or lacks its norm")
+    kind = out.dtype if out is not None else (y.dtype if y is not None else (dtype or torch.float32))
+    post_a, post_w, post_b = _tanh_norm_args("tanh_norm_fold", post if y is not None else None, hidden)
+    pre_a, pre_w, pre_b = _tanh_norm_args("tanh_norm_fold", pre if out is not None else None, hidden)
+    _rowwise.call("zi_tanh_norm_fold", ptr(h), ptr(y), c_int(dtype_code(kind)), post_a, post_w, post_b, pre_a, pre_w, pre_b, ptr(out),
+                  ptr(row_idx), c_int(rows), c_int(hidden), c_int(1 if write_h else 0), stream())
+
+
+def rms_pair_mean(x: torch.Tensor, z: torch.Tensor, wx: torch.Tensor, wz: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """``out = (U(x) * wx + U(z) * wz) / 2`` with ``U(v) = v / sqrt(mean(v^2) + eps)`` over a row (float32 inside; ``wx``, ``wz``
+    float32)."""
+    need_cuda(x, z, wx, wz, out)
+    need_contiguous("x", x), need_contiguous("z", z), need_contiguous("out", out), need_contiguous("wx", wx), need_contiguous("wz", wz)
+    rows, hidden = x.shape
+    if z.shape != x.shape or out.shape != x.shape or not (x.dtype == z.dtype == out.dtype) or wx.dtype != torch.float32 \
+            or wz.dtype != torch.float32 or wx.numel() != hidden or wz.numel() != hidden:
+        raise KernelError(f"rms_pair_mean: x {tuple(x.shape)}, z {tuple(z.shape)}, out {tuple(out.shape)} and the float32 weights do not agree")
+    _rowwise.call("zi_rms_pair_mean", ptr(x), ptr(z), c_int(dtype_code(x.dtype)), ptr(wx), ptr(wz), ptr(out), c_float(eps), c_int(rows),
+                  c_int(hidden), stream())
+
+
+def poly_norm(z: torch.Tensor, coeffs, eps: float, out: torch.Tensor) -> None:
+    """``out = c1 U(z) + c2 U(z^2) + c3 U(z^3) + c0`` with ``coeffs = (c1, c2, c3, c0)``, powers entry by entry and ``U(v) = v /
+    sqrt(mean(v^2) + eps)`` over a row (float32 inside); rows of ``z`` may be strided."""
+    need_cuda(z, out)
+    need_contiguous("out", out)
+    rows, width = z.shape
+    if z.stride(1) != 1 or out.shape != z.shape or out.dtype != z.dtype or len(coeffs) != 4:
+        raise KernelError(f"poly_norm: z {tuple(z.shape)}, out {tuple(out.shape)} and four coefficients do not agree")
+    c1, c2, c3, c0 = (float(c) for c in coeffs)
+    _rowwise.call("zi_poly_norm", ptr(z), c_int(dtype_code(z.dtype)), c_ll(z.stride(0)), ptr(out), c_int(rows), c_int(width), c_float(c1),
+                  c_float(c2), c_float(c3), c_float(c0), c_float(eps), stream())
+
+
+def row_gate(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[n] = sigmoid(x[n] . w)`` in float32 (``out`` float32, one entry per row; rows of ``x`` may be strided)."""
+    need_cuda(x, w, out)
+    need_contiguous("w", w), need_contiguous("out", out)
+    rows, k = x.shape
+    if x.stride(1) != 1 or w.numel() != k or out.dtype != torch.float32 or out.numel() != rows:
+        raise KernelError(f"row_gate: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+    _rowwise.call("zi_row_gate", ptr(x), c_int(dtype_code(x.dtype)), c_ll(x.stride(0)), ptr(w), c_int(dtype_code(w.dtype)), ptr(out),
+                  c_int(rows), c_int(k), stream())

@@ -20,7 +20,9 @@ heads of the query are then ``row_dim`` wide, the larger of the two sizes rounde
 a head's own entries is zero, which changes no score and no output), ``shared_kv`` (the layer has no key and value
 projections: it reads the cache that another layer's call wrote, with its own queries, window and everything else) and
 ``cache_window`` (the window the cache keeps pages for, where layers that read this layer's cache look further back than
-the layer itself; ``"own"``: the layer's window, None: all keys).
+the layer itself; ``"own"``: the layer's window, None: all keys) and ``head_scale`` (the local name of a tensor with one
+number per query head that multiplies that head's scores, ``s = q . k * scale * t_h``; the query head is multiplied by it, in
+float32, as the position rule's kernel writes it, so it goes with ``v_head_dim`` given).
 """
 from __future__ import annotations
 
@@ -47,7 +49,7 @@ class AttentionMixer(Mixer):
                  position: PartSpec, qkv_bias: bool = True, out_bias: bool = False,
                  scale: Optional[float] = None, window: Optional[int] = None, value_from_key: bool = False,
                  unit_sink: bool = False, names: Optional[Mapping[str, str]] = None, softcap: Optional[float] = None,
-                 v_head_dim: Optional[int] = None, shared_kv: bool = False, cache_window="own"):
+                 v_head_dim: Optional[int] = None, shared_kv: bool = False, cache_window="own", head_scale: Optional[str] = None):
         if num_heads <= 0 or num_kv_heads <= 0 or num_heads % num_kv_heads:
             raise ValueError(f"attention: {num_heads} query heads cannot share {num_kv_heads} key/value heads")
         if softcap is not None and not softcap > 0.0:
@@ -55,6 +57,10 @@ class AttentionMixer(Mixer):
         if v_head_dim is not None and (v_head_dim <= 0 or position.kind != "rope_span" or value_from_key):
             raise ValueError("attention: value heads of a size of their own need a positive size, the position rule 'rope_span' "
                              "and a value projection")
+        if head_scale is not None and v_head_dim is None:
+            raise ValueError("attention: a factor per query head goes with v_head_dim given (the size of the value heads)")
+        self.head_scale_name = head_scale
+        self.head_scale: Optional[torch.Tensor] = None
         if shared_kv and (value_from_key or qkv_bias):
             raise ValueError("attention: a layer without key and value projections has neither their biases nor keys as values")
         # a rule that turns a span of the head (its own kernel) takes steps of 8; the rotate-half kernels steps of 16
@@ -126,6 +132,8 @@ class AttentionMixer(Mixer):
             specs.update({nm[r + "_bias"]: TensorSpec((self._width(r),)) for r in roles})
         if self.out_bias:
             specs[nm["o_bias"]] = TensorSpec((h,))
+        if self.head_scale_name is not None:
+            specs[self.head_scale_name] = TensorSpec((self.num_heads,), init=("one_plus_normal", 0.05))
         return specs
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
@@ -165,6 +173,8 @@ class AttentionMixer(Mixer):
             self.b_o = tensors[nm["o_bias"]].contiguous()
         if self.unit_sink:
             self.sinks = torch.zeros(self.num_heads, dtype=torch.float32, device=self.w_o.device)
+        if self.head_scale_name is not None:
+            self.head_scale = tensors[self.head_scale_name].float().contiguous()       # scores are float32
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CallCacheView, owns_cache: bool) -> torch.Tensor:
         out = ctx.empty(x.shape[0], self.hidden_size)
@@ -190,7 +200,8 @@ class AttentionMixer(Mixer):
             q = ctx.empty(n, self.num_heads, self.row_dim)
             if self._wide:
                 self.position.rotate_append(proj, q, cache, ctx, self.num_heads, self.num_kv_heads, self.head_dim,
-                                            write_kv=owns_cache, v_dim=self.v_head_dim, row_dim=self.row_dim)
+                                            write_kv=owns_cache, v_dim=self.v_head_dim, row_dim=self.row_dim,
+                                            q_head_scale=self.head_scale)
             else:
                 self.position.rotate_append(proj, q, cache, ctx, self.num_heads, self.num_kv_heads, self.head_dim, write_kv=False)
             attn = ctx.empty(n, self.num_heads * self.row_dim)

@@ -73,6 +73,9 @@ class ResidualStream:
     h: torch.Tensor
     delta: Optional[torch.Tensor] = None
     delta_scale: float = 1.0     # the factor on ``delta`` when a norm folds it in: ``h += delta_scale * delta`` (float32)
+    # the norm that ``delta`` passes before it joins ``h`` (arrangements with a norm after every sublayer): whoever folds
+    # ``delta`` applies it first, ``h += delta_norm(delta)``; None: ``delta`` joins as it is
+    delta_norm: Optional["Norm"] = None
     # ``h`` rounded to the step's type, where the kernel that last changed ``h`` made that copy on its way (arrangements
     # whose sublayers read the stream itself); whoever changes ``h`` otherwise sets it to None
     rounded: Optional[torch.Tensor] = None

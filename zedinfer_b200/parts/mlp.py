@@ -108,6 +108,48 @@ class SquaredReluMLP(FeedForward):
         return ops.linear_for_residual(self._activation(x, ctx), self.w_down, None)
 
 
+@register_feed_forward("poly_norm_mlp")
+class PolyNormMLP(FeedForward):
+    """``down(P(up(x)))`` with ``P(z) = c1 U(z) + c2 U(z^2) + c3 U(z^3) + c0``: powers entry by entry, each divided by its own
+    root mean square over the row, ``U(v) = v / sqrt(mean(v^2) + eps)`` (float32).  The four numbers come from one tensor
+    ``[c1, c2, c3, c0]``; no gate, no biases."""
+    capture_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, eps: float, up_name: str = "up", down_name: str = "down",
+                 coeff_name: str = "act"):
+        if hidden_size <= 0 or intermediate_size <= 0:
+            raise ValueError("poly_norm_mlp: sizes must be positive")
+        if not eps > 0.0:
+            raise ValueError(f"poly_norm_mlp: eps={eps} must be positive")
+        self.hidden_size, self.intermediate_size, self.eps = int(hidden_size), int(intermediate_size), float(eps)
+        self.up_name, self.down_name, self.coeff_name = up_name, down_name, coeff_name
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+        self.coeffs = (1.0, 0.0, 0.0, 0.0)
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.up_name: TensorSpec((self.intermediate_size, self.hidden_size)),
+                self.down_name: TensorSpec((self.hidden_size, self.intermediate_size)),
+                self.coeff_name: TensorSpec((4,), init=("normal", 0.5))}
+
+    def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_up = tensors[self.up_name].contiguous()
+        self.w_down = tensors[self.down_name].contiguous()
+        self.coeffs = tuple(float(c) for c in tensors[self.coeff_name].float().cpu().tolist())     # read once, at load
+
+    def _activation(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        z = ctx.empty(x.shape[0], self.intermediate_size)
+        ops.linear(x, self.w_up, None, z)
+        act = ctx.empty(x.shape[0], self.intermediate_size)
+        ops.poly_norm(z, self.coeffs, self.eps, act)
+        return act
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        out = ctx.empty(x.shape[0], self.hidden_size)
+        ops.linear(self._activation(x, ctx), self.w_down, None, out)
+        return out
+
+
 @register_feed_forward("clamped_gated_mlp")
 class ClampedGatedMLP(FeedForward):
     """``down(g * sigmoid(slope * g) * (u + up_offset))`` with ``g = min(gate(x), limit)``, ``u = clamp(up(x), -limit,

@@ -153,20 +153,23 @@ class SpanRotaryPosition(PositionEncoding):
 
     def rotate_append(self, qkv: torch.Tensor, q_out: torch.Tensor, cache: CallCacheView, ctx: StepContext,
                       n_heads: int, n_kv_heads: int, head_dim: int, write_kv: bool, value_from_key: bool = False,
-                      v_dim: Optional[int] = None, row_dim: Optional[int] = None) -> None:
+                      v_dim: Optional[int] = None, row_dim: Optional[int] = None,
+                      q_head_scale: Optional[torch.Tensor] = None) -> None:
         """``v_dim``: the value heads' size where it differs from ``head_dim``; ``row_dim``: the width of the cache's rows
-        and of the heads of ``q_out`` where that is more than a head (the rest is written as zero)."""
+        and of the heads of ``q_out`` where that is more than a head (the rest is written as zero); ``q_head_scale``
+        (float32, one per query head): a factor on every query head as it is written."""
         if head_dim != self.head_dim:
             raise ValueError(f"rope_span was built for head_dim={self.head_dim}, the mixer has {head_dim}")
         v_dim = head_dim if v_dim is None else v_dim
         row_dim = head_dim if row_dim is None else row_dim
-        if self.scaling is not None or self.unit_rms_eps is not None or v_dim != head_dim or row_dim != head_dim or not self.dims:
+        if (self.scaling is not None or self.unit_rms_eps is not None or v_dim != head_dim or row_dim != head_dim or not self.dims
+                or q_head_scale is not None):
             if value_from_key:
                 raise ValueError("rope_span: unturned keys as values go with the plain span only")
             ops.rotary_norm(qkv, q_out, ctx.positions, self.table(qkv.device) if self.dims else None, self.magnitude, n_heads,
                             n_kv_heads, head_dim, v_dim, row_dim, self.dims, self.interleaved, self.unit_rms_eps,
                             cache=cache if write_kv else None, tables=ctx.tables[cache.group] if write_kv else None,
-                            tok_seg=ctx.tok_seg if write_kv else None)
+                            tok_seg=ctx.tok_seg if write_kv else None, q_head_scale=q_head_scale)
             return
         if not write_kv:
             ops.rotary(qkv, q_out, ctx.positions, self.table(qkv.device), n_heads, 0, head_dim, self.offset, self.dims,
