@@ -231,3 +231,10 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], trace: Lis
         if trace is not None:
             trace.append(x.clone())
     return tanh_norm(x, w, "final.norm") @ w["embed"].T
+
+
+def greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    seq = list(prompt)
+    for _ in range(n_new):
+        seq.append(int(torch.argmax(forward(cfg, w, seq)[-1])))
+    return seq[len(prompt):]
