@@ -377,6 +377,27 @@ def kevatar_config(width, heads, ff, window, layers, vocab, dim=128, **_):
             "embedding": {"scale": float(width) ** 0.5}, "token_side": {"dim": 64}, "layers": out}
 
 
+def sumitar_config(width, heads, ff, window, layers, vocab, experts, top, expert_ff, shared_ff, dim=128, **_):
+    """The Sumitar design at the same width, layers, heads, head size, window and vocabulary: layers of two mixers side by side
+    (windowed attention with grouped heads, half of every head turned, beside forget-gate heads of 64 x 128) and delta-rule
+    layers (heads of 128 x 128, four taps) by turns; feed-forwards dense (two matrices of the inner width `ff`, as many weights
+    as the three of Qwen2's beside it) and routed (`experts` of `expert_ff` plus two that return their input, `top` chosen, a
+    gated shared expert) by turns."""
+    kv = 2 if heads <= 12 else 4
+    left = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": window}, "rot": {"base": 1000000.0, "dims": dim // 2},
+            "scale": dim ** -0.5}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "identity": 2, "top": top}, "shared": {"ff": shared_ff}}
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            mixer = {"type": "parallel", "mixer": {"left": left, "right": {"heads": heads, "dim": dim // 2, "vdim": dim}}}
+        else:
+            mixer = {"type": "delta", "mixer": {"heads": heads, "kv_heads": heads, "dim": dim, "vdim": dim, "conv": 4}}
+        out.append(dict(mixer, mlp=dense if i % 4 in (0, 3) else moe))
+    return {"architecture": "Sumitar", "vocab": vocab, "width": width, "max_positions": CONTEXT, "norm": {"eps": 1e-5}, "layers": out}
+
+
 def measure_design(cfg, vocab, batch, steps, warmup):
     """Prefill of PROMPT_LEN tokens in one step and decode of `batch` requests through the captured greedy step."""
     import torch
@@ -434,6 +455,17 @@ def design_comparison(args):
     rows = []
     for name, size in DESIGN_SIZES.items():
         q = {k: size[k] for k in ("width", "heads", "ff", "window", "layers", "vocab")}
+        if args.designs == "sumitar":
+            # the design beside Kevatar, its closest relative (windowed attention and matrix states), and beside Qwen2
+            qwen = measure_design(qwen2_config_like(**q), size["vocab"], args.batch, steps, warmup)
+            kev = measure_design(kevatar_config(**q), size["vocab"], args.batch, steps, warmup)
+            sm = measure_design(sumitar_config(**size), size["vocab"], args.batch, steps, warmup)
+            rows.append({"size": name, "shape": size, "sumitar": sm, "kevatar": kev, "qwen2_equal_size": qwen,
+                         "prefill_ratio_to_kevatar": round(sm["prefill_tokens_per_s"] / kev["prefill_tokens_per_s"], 3),
+                         "decode_ratio_to_kevatar": round(sm["decode_tokens_per_s"] / kev["decode_tokens_per_s"], 3),
+                         "prefill_ratio": round(sm["prefill_tokens_per_s"] / qwen["prefill_tokens_per_s"], 3),
+                         "decode_ratio": round(sm["decode_tokens_per_s"] / qwen["decode_tokens_per_s"], 3)})
+            continue
         if args.designs == "kevatar":
             # the design beside the model it is closest to: dense feed-forward, grouped heads, a window
             qwen = measure_design(qwen2_config_like(**q), size["vocab"], args.batch, steps, warmup)
@@ -548,10 +580,11 @@ def main():
     ap.add_argument("--layers", type=int, default=MODEL_1P5B["num_hidden_layers"],
                     help="fewer layers than the model has (same layer sizes), where memory or time needs it")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
-    ap.add_argument("--designs", nargs="?", const="baselix", default=None, choices=["baselix", "gibalorn", "kevatar"],
+    ap.add_argument("--designs", nargs="?", const="baselix", default=None, choices=["baselix", "gibalorn", "kevatar", "sumitar"],
                     help="instead of the default workload: prefill and decode of the Baselix design at layer sizes of real "
                          "models (random weights) beside Qwen2 at equal size; '--designs gibalorn' also runs the Gibalorn "
-                         "design at those sizes; '--designs kevatar' runs the Kevatar design beside Qwen2 alone")
+                         "design at those sizes; '--designs kevatar' runs the Kevatar design beside Qwen2 alone; '--designs sumitar' the "
+                         "Sumitar design beside Kevatar and Qwen2")
     args = ap.parse_args()
 
     if args.impl == "reference":

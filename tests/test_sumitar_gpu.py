@@ -66,6 +66,17 @@ def test_the_tanh_norm_on_both_sides_of_a_float32_stream(dtype, rows, hidden):
     h = h0.clone().to(DEV)
     ops.tanh_norm_fold(h, y.to(DEV), dev(post), None, None)
     assert rel_err(h, want_h) < 2e-6
+    # two branches joined on the way: the same as joining them first (up to that step's rounding)
+    y2 = (torch.randn(rows, hidden, generator=g) * 0.5).to(dtype)
+    w1, w2, eps = 1 + 0.3 * torch.randn(hidden, generator=g), 1 + 0.3 * torch.randn(hidden, generator=g), 1e-5
+    joined = 0.5 * (SP.rms_unit(y.double(), eps) * w1.double() + SP.rms_unit(y2.double(), eps) * w2.double())
+    want_j = h0.double() + norm(joined, post)
+    h, out = h0.clone().to(DEV), torch.empty(rows, hidden, dtype=dtype, device=DEV)
+    ops.tanh_norm_fold(h, y.to(DEV), dev(post), dev(pre), out, join=(y2.to(DEV), w1.to(DEV), w2.to(DEV), eps))
+    assert rel_err(h, want_j) < 2e-6 and rel_err(out, norm(want_j, pre)) < tol
+    h, out = h0.clone().to(DEV), torch.empty(3, hidden, dtype=dtype, device=DEV)
+    ops.tanh_norm_fold(h, y.to(DEV), dev(post), dev(pre), out, row_idx=idx.to(DEV), join=(y2.to(DEV), w1.to(DEV), w2.to(DEV), eps))
+    assert torch.equal(h.cpu(), h0) and rel_err(out, norm(want_j, pre)[idx.long()]) < tol
     # the norm on its own, of rows of either type
     for x in (h0, y):
         out = torch.empty(rows, hidden, dtype=dtype, device=DEV)

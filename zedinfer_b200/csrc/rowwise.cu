@@ -710,6 +710,18 @@ ZI_EXPORT int zi_gelu_mul_rows(const void* t, int dtype, long long ldt, const vo
 // row = row_idx[r] where row_idx is given (then h is not written), else r.  h float32; y and out of the step's type; w, b
 // float32.  Entry by entry, so a row's result depends on nothing else.
 // ---------------------------------------------------------------------------------------
+// Three block sums at once; scratch holds at least 96 floats.  The order of additions depends on the block size alone.
+__device__ __forceinline__ void block_sum3(float& a, float& b, float& c, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    a = warp_sum(a); b = warp_sum(b); c = warp_sum(c);
+    __syncthreads();
+    if (lane == 0) { scratch[warp] = a; scratch[32 + warp] = b; scratch[64 + warp] = c; }
+    __syncthreads();
+    a = warp_sum(lane < nwarps ? scratch[lane] : 0.0f);
+    b = warp_sum(lane < nwarps ? scratch[32 + lane] : 0.0f);
+    c = warp_sum(lane < nwarps ? scratch[64 + lane] : 0.0f);
+}
+
 struct TanhNormArgs { float a; const float* w; const float* b; };
 
 template <typename T>
@@ -774,6 +786,50 @@ ZI_EXPORT int zi_tanh_norm_fold(float* h, const void* y, int dtype, float post_a
     return zi_check_launch("tanh_norm_fold");
 }
 
+// The same fold for a pending output of two branches that read the same input and are joined on the way:
+//     y = (U(y1) * w1 + U(y2) * w2) / 2,   U(v) = v / sqrt(mean(v^2) + eps) over the row;   v = h[row] + N(y; post);  ...
+// One block per row; the joined row never leaves the chip.
+template <typename T>
+__global__ void __launch_bounds__(256)
+tanh_norm_fold_pair_kernel(float* __restrict__ h, const T* __restrict__ y1, const T* __restrict__ y2, const float* __restrict__ w1,
+                           const float* __restrict__ w2, float eps, TanhNormArgs post, TanhNormArgs pre, T* __restrict__ out,
+                           const int* __restrict__ row_idx, int write_h, int hidden) {
+    extern __shared__ float fp_row[];                    // y1's row, then y2's
+    __shared__ float scratch[96];
+    const size_t r = blockIdx.x, row = row_idx ? (size_t)row_idx[r] : r;
+    float s1 = 0.0f, s2 = 0.0f, unused = 0.0f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        const float a = to_f32<T>(y1[row * hidden + j]), b = to_f32<T>(y2[row * hidden + j]);
+        fp_row[j] = a; fp_row[hidden + j] = b;
+        s1 = fmaf(a, a, s1); s2 = fmaf(b, b, s2);
+    }
+    block_sum3(s1, s2, unused, scratch);
+    const float r1 = 1.0f / sqrtf(s1 / (float)hidden + eps), r2 = 1.0f / sqrtf(s2 / (float)hidden + eps);
+    float* hr = h + row * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        const float joined = 0.5f * ((fp_row[j] * r1) * w1[j] + (fp_row[hidden + j] * r2) * w2[j]);
+        const float v = hr[j] + (tanhf(post.a * joined) * post.w[j] + post.b[j]);
+        if (write_h) hr[j] = v;
+        if (out) out[r * hidden + j] = from_f32<T>(tanhf(pre.a * v) * pre.w[j] + pre.b[j]);
+    }
+}
+
+ZI_EXPORT int zi_tanh_norm_fold_pair(float* h, const void* y1, const void* y2, int dtype, const float* w1, const float* w2, float eps, float post_a,
+                                     const float* post_w, const float* post_b, float pre_a, const float* pre_w, const float* pre_b, void* out,
+                                     const int* row_idx, int rows, int hidden, int write_h, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || (size_t)hidden * 2 * sizeof(float) > 48 * 1024) return zi_fail("tanh_norm_fold_pair: hidden=%d is not supported", hidden);
+    if (!y1 || !y2 || !w1 || !w2 || !post_w || !post_b) return zi_fail("tanh_norm_fold_pair: two branches, their weights and the norm that follows are needed");
+    if (out && (!pre_w || !pre_b)) return zi_fail("tanh_norm_fold_pair: an output needs the norm that makes it");
+    if (row_idx && write_h) return zi_fail("tanh_norm_fold_pair: chosen rows leave the stream as it is");
+    const TanhNormArgs post{post_a, post_w, post_b}, pre{pre_a, pre_w, pre_b};
+    ZI_DISPATCH(dtype, T, {
+        tanh_norm_fold_pair_kernel<T><<<rows, hidden >= 2048 ? 256 : 128, (size_t)hidden * 2 * sizeof(float), stream>>>(
+            h, (const T*)y1, (const T*)y2, w1, w2, eps, post, pre, (T*)out, row_idx, write_h, hidden);
+    });
+    return zi_check_launch("tanh_norm_fold_pair");
+}
+
 // out = tanh(a x) * w + b for rows of any of the two types (a norm called on its own).
 template <typename TX, typename T>
 __global__ void tanh_norm_kernel(const TX* __restrict__ x, TanhNormArgs nm, T* __restrict__ out, int hidden, size_t total) {
@@ -835,11 +891,45 @@ ZI_EXPORT int zi_rms_pair_mean(const void* x, const void* z, int dtype, const fl
 //     out = c1 U(z) + c2 U(z^2) + c3 U(z^3) + c0,   U(v) = v / sqrt(mean(v^2) + eps),  powers entry by entry
 // float32 inside.  One block per row; rows of z may be strided.
 // ---------------------------------------------------------------------------------------
+// Eight entries per access: width and ldz multiples of 8, pointers on 16-byte boundaries.  The sums run per thread over its
+// own entries in rising order and then over the block, as in the scalar form but dealt otherwise: which form runs depends on
+// the sizes and on where the buffers start, never on the rows of the step.
+template <typename T>
+__global__ void __launch_bounds__(256)
+poly_norm_vec8_kernel(const T* __restrict__ z, long long ldz, T* __restrict__ out, int width, float c1, float c2, float c3, float c0, float eps) {
+    extern __shared__ __align__(16) float pn_row[];
+    __shared__ float scratch[96];
+    const size_t n = blockIdx.x;
+    float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
+    for (int j = threadIdx.x * 8; j < width; j += blockDim.x * 8) {
+        float v[8];
+        load8(z + n * ldz + j, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float v2 = v[e] * v[e], v3 = v2 * v[e];
+            s2 += v2; s4 = fmaf(v2, v2, s4); s6 = fmaf(v3, v3, s6);
+        }
+        store8(pn_row + j, v);
+    }
+    block_sum3(s2, s4, s6, scratch);
+    const float r1 = 1.0f / sqrtf(s2 / (float)width + eps), r2 = 1.0f / sqrtf(s4 / (float)width + eps), r3 = 1.0f / sqrtf(s6 / (float)width + eps);
+    for (int j = threadIdx.x * 8; j < width; j += blockDim.x * 8) {
+        float v[8], o[8];
+        load8(pn_row + j, v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float v2 = v[e] * v[e], v3 = v2 * v[e];
+            o[e] = c1 * (v[e] * r1) + c2 * (v2 * r2) + c3 * (v3 * r3) + c0;
+        }
+        store8(out + n * width + j, o);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 poly_norm_kernel(const T* __restrict__ z, long long ldz, T* __restrict__ out, int width, float c1, float c2, float c3, float c0, float eps) {
-    extern __shared__ float pn_row[];
-    __shared__ float scratch[32];
+    extern __shared__ __align__(16) float pn_row[];
+    __shared__ float scratch[96];
     const size_t n = blockIdx.x;
     float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
     for (int j = threadIdx.x; j < width; j += blockDim.x) {
@@ -847,9 +937,7 @@ poly_norm_kernel(const T* __restrict__ z, long long ldz, T* __restrict__ out, in
         pn_row[j] = v;
         s2 += v2; s4 = fmaf(v2, v2, s4); s6 = fmaf(v3, v3, s6);
     }
-    s2 = block_sum(s2, scratch);
-    s4 = block_sum(s4, scratch);
-    s6 = block_sum(s6, scratch);
+    block_sum3(s2, s4, s6, scratch);
     const float r1 = 1.0f / sqrtf(s2 / (float)width + eps), r2 = 1.0f / sqrtf(s4 / (float)width + eps), r3 = 1.0f / sqrtf(s6 / (float)width + eps);
     for (int j = threadIdx.x; j < width; j += blockDim.x) {
         const float v = pn_row[j], v2 = v * v, v3 = v2 * v;
@@ -862,12 +950,14 @@ ZI_EXPORT int zi_poly_norm(const void* z, int dtype, long long ldz, void* out, i
     if (rows <= 0) return 0;
     const size_t smem = (size_t)width * sizeof(float);
     if (width <= 0 || smem > 200 * 1024) return zi_fail("poly_norm: width=%d is not supported", width);
+    const bool vec = width % 8 == 0 && ldz % 8 == 0 && (((size_t)z | (size_t)out) & 31) == 0;
     ZI_DISPATCH(dtype, T, {
         if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(poly_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaError_t e = cudaFuncSetAttribute(vec ? poly_norm_vec8_kernel<T> : poly_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return zi_fail("poly_norm: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
         }
-        poly_norm_kernel<T><<<rows, 256, smem, stream>>>((const T*)z, ldz, (T*)out, width, c1, c2, c3, c0, eps);
+        if (vec) poly_norm_vec8_kernel<T><<<rows, 256, smem, stream>>>((const T*)z, ldz, (T*)out, width, c1, c2, c3, c0, eps);
+        else poly_norm_kernel<T><<<rows, 256, smem, stream>>>((const T*)z, ldz, (T*)out, width, c1, c2, c3, c0, eps);
     });
     return zi_check_launch("poly_norm");
 }

@@ -1462,11 +1462,14 @@ def tanh_norm(x: torch.Tensor, alpha: float, w: torch.Tensor, b: torch.Tensor, o
 
 
 def tanh_norm_fold(h: torch.Tensor, y: Optional[torch.Tensor], post, pre, out: Optional[torch.Tensor],
-                   row_idx: Optional[torch.Tensor] = None, write_h: bool = True, dtype: Optional[torch.dtype] = None) -> None:
+                   row_idx: Optional[torch.Tensor] = None, write_h: bool = True, dtype: Optional[torch.dtype] = None,
+                   join=None) -> None:
     """The tanh norm ``N(v; alpha, w, b) = tanh(alpha v) * w + b`` on both sides of the float32 stream ``h``: ``v = h + N(y;
     post)`` where a branch's output ``y`` is pending (``y`` None: ``v = h``), ``h = v`` where ``write_h``, ``out = N(v; pre)``
     where ``out`` is given.  ``post``, ``pre``: (alpha, float32 weight, float32 bias) or None.  With ``row_idx`` output row r
-    comes from row ``row_idx[r]`` and ``h`` is left as it is."""
+    comes from row ``row_idx[r]`` and ``h`` is left as it is.  ``join = (y2, w1, w2, eps)``: the pending output is that of two
+    branches joined on the way, ``(U(y) * w1 + U(y2) * w2) / 2`` with ``U(v) = v / sqrt(mean(v^2) + eps)`` over a row and float32
+    weights (what :func:`rms_pair_mean` computes, without the rounding in between)."""
     need_cuda(h, y, out, row_idx)
     need_contiguous("h", h)
     if h.dtype != torch.float32 or h.dim() != 2:
@@ -1483,6 +1486,18 @@ def tanh_norm_fold(h: torch.Tensor, y: Optional[torch.Tensor], post, pre, out: O
     kind = out.dtype if out is not None else (y.dtype if y is not None else (dtype or torch.float32))
     post_a, post_w, post_b = _tanh_norm_args("tanh_norm_fold", post if y is not None else None, hidden)
     pre_a, pre_w, pre_b = _tanh_norm_args("tanh_norm_fold", pre if out is not None else None, hidden)
+    if join is not None:
+        y2, w1, w2, eps = join
+        need_cuda(y2, w1, w2)
+        if y is None or y2.shape != y.shape or y2.dtype != y.dtype or not y2.is_contiguous():
+            raise KernelError("tanh_norm_fold: the second branch must be contiguous, of the first one's shape and type")
+        for t in (w1, w2):
+            if t.dtype != torch.float32 or t.numel() != hidden or not t.is_contiguous():
+                raise KernelError(f"tanh_norm_fold: the branches' weights must be contiguous float32 with {hidden} entries")
+        _rowwise.call("zi_tanh_norm_fold_pair", ptr(h), ptr(y), ptr(y2), c_int(dtype_code(kind)), ptr(w1), ptr(w2), c_float(eps), post_a,
+                      post_w, post_b, pre_a, pre_w, pre_b, ptr(out), ptr(row_idx), c_int(rows), c_int(hidden),
+                      c_int(1 if write_h else 0), stream())
+        return
     _rowwise.call("zi_tanh_norm_fold", ptr(h), ptr(y), c_int(dtype_code(kind)), post_a, post_w, post_b, pre_a, pre_w, pre_b, ptr(out),
                   ptr(row_idx), c_int(rows), c_int(hidden), c_int(1 if write_h else 0), stream())
 

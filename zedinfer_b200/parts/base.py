@@ -76,6 +76,10 @@ class ResidualStream:
     # the norm that ``delta`` passes before it joins ``h`` (arrangements with a norm after every sublayer): whoever folds
     # ``delta`` applies it first, ``h += delta_norm(delta)``; None: ``delta`` joins as it is
     delta_norm: Optional["Norm"] = None
+    # ``delta`` is the first of two branch outputs that are joined as they are folded: (the second output, the first one's
+    # float32 weight, the second one's, eps) for ``(U(delta) * w1 + U(second) * w2) / 2``, ``U`` the division by the root mean
+    # square over a row; the joined row then passes ``delta_norm``.  None: ``delta`` is the whole branch
+    delta_join: Optional[tuple] = None
     # ``h`` rounded to the step's type, where the kernel that last changed ``h`` made that copy on its way (arrangements
     # whose sublayers read the stream itself); whoever changes ``h`` otherwise sets it to None
     rounded: Optional[torch.Tensor] = None

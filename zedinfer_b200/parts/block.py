@@ -14,7 +14,6 @@ from __future__ import annotations
 
 from typing import Mapping
 
-from .. import ops
 from ..cache.manager import CallCacheView
 from .base import Block, ResidualStream, StepContext, register_block
 
@@ -86,11 +85,12 @@ class SandwichNormBlock(Block):
 
     ``ffn`` with ``norm2`` and ``norm2b`` is optional.  A branch's output stays pending in the stream together with the norm
     that follows it (``ResidualStream.delta_norm``) until the next norm before a sublayer (or the model's last norm) folds both
-    into the float32 residual, so every sublayer costs one norm kernel.
+    into the float32 residual, so every sublayer costs one norm kernel (``ops.tanh_norm_fold``).
 
     With a second mixer (role ``mixer2``, a cache of its own) the two read the same normed input and their outputs are
     joined as ``(U(y1) * w1 + U(y2) * w2) / 2``, ``U`` the division by the root mean square over the row, the weights those
-    of the norms ``mix_out`` and ``mix2_out`` (built with ``float32_weight``)."""
+    of the norms ``mix_out`` and ``mix2_out`` (built with ``float32_weight``); the join rides in the same pending state
+    (``ResidualStream.delta_join``) and happens inside the kernel that folds (``ops.rms_pair_mean`` is the join on its own)."""
     capture_safe = True
 
     def __init__(self, parts):
@@ -114,14 +114,13 @@ class SandwichNormBlock(Block):
         normed = ctx.empty(n, hidden)
         self.norms["norm1"].forward_residual(stream, normed)
         y = self.mixer.forward(normed, ctx, caches["mixer"], owns_cache)
+        stream.delta, stream.delta_norm, stream.delta_scale, stream.delta_join = y, self.norms["norm1b"], 1.0, None
         if self.mixer2 is not None:
+            # the two outputs are joined by whoever folds them into the stream (one kernel for join, norm, add and next norm)
             y2 = self.mixer2.forward(normed, ctx, caches["mixer2"], owns_cache)
-            joined = ctx.empty(n, hidden)
-            ops.rms_pair_mean(y, y2, self.norms["mix_out"].weight, self.norms["mix2_out"].weight, self.norms["mix_out"].eps, joined)
-            y = joined
-        stream.delta, stream.delta_norm, stream.delta_scale = y, self.norms["norm1b"], 1.0
+            stream.delta_join = (y2, self.norms["mix_out"].weight, self.norms["mix2_out"].weight, self.norms["mix_out"].eps)
         if self.ffn is None:
             return
         normed2 = ctx.empty(n, hidden)
         self.norms["norm2"].forward_residual(stream, normed2)
-        stream.delta, stream.delta_norm, stream.delta_scale = self.ffn.forward(normed2, ctx), self.norms["norm2b"], 1.0
+        stream.delta, stream.delta_norm, stream.delta_scale, stream.delta_join = self.ffn.forward(normed2, ctx), self.norms["norm2b"], 1.0, None

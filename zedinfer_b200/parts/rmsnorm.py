@@ -40,7 +40,7 @@ class RMSNorm(Norm):
 
     def forward_residual(self, stream: ResidualStream, out: torch.Tensor,
                          row_idx: Optional[torch.Tensor] = None) -> None:
-        if stream.delta is not None and stream.delta_norm is not None:
+        if stream.delta is not None and (stream.delta_norm is not None or stream.delta_join is not None):
             raise RuntimeError("rmsnorm cannot fold a branch output that must pass a norm of its own first")
         ops.add_rmsnorm(stream.h, stream.delta, self.weight, self.eps, out, row_idx=row_idx,
                         write_residual=row_idx is None, delta_scale=stream.delta_scale)

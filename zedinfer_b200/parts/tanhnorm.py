@@ -3,7 +3,8 @@ float32.  It computes no mean and no variance, so it needs no epsilon.
 
 It serves arrangements that norm a sublayer's input and its output (``sandwich_norm``): the norm *after* a sublayer rides
 with the sublayer's output in the stream (``ResidualStream.delta_norm``) until the next norm *before* a sublayer folds
-both into the float32 residual, one kernel for ``h += N_after(y); out = N_before(h)``."""
+both into the float32 residual, one kernel for ``h += N_after(y); out = N_before(h)``.  Where ``y`` is the output of two branches
+that are joined by their unit rows (``ResidualStream.delta_join``), the same kernel joins them on the way."""
 from __future__ import annotations
 
 from typing import Dict, Mapping, Optional
@@ -55,11 +56,12 @@ class TanhNorm(Norm):
             if stream.delta.dim() != 2 or not isinstance(stream.delta_norm, TanhNorm):
                 raise RuntimeError("tanh_norm folds a branch output [tokens, hidden] that brings the tanh norm that follows it")
             post = stream.delta_norm.params()
-        ops.tanh_norm_fold(stream.h, stream.delta, post, self.params(), out, row_idx=row_idx, write_h=row_idx is None)
+        ops.tanh_norm_fold(stream.h, stream.delta, post, self.params(), out, row_idx=row_idx, write_h=row_idx is None,
+                           join=stream.delta_join if stream.delta is not None else None)
         if row_idx is None:
             if stream.delta is not None:
                 stream.rounded = None           # h has changed
-            stream.delta, stream.delta_norm = None, None
+            stream.delta, stream.delta_norm, stream.delta_join = None, None, None
 
     def forward_branch(self, stream: ResidualStream, y: torch.Tensor, ctx: StepContext) -> None:
         """``h += tanh(alpha y) * w + b`` (float32) at once, nothing left pending."""
