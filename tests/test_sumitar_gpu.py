@@ -653,14 +653,15 @@ def test_greedy_generation_equals_plain(models, name, graphs):
     assert st["live_requests"] == 0 and st["free_pages"] == st["pages_per_group"]
 
 
-@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
-def test_trace_program_on_a_sumitar_folder(models, tmp_path, dtype):
-    cfg, _ = ST.CONFIGS["B"]
+@pytest.mark.parametrize("name,dtype", [("B", "bfloat16"), ("B", "float32"), ("D", "float32"), ("E", "bfloat16")])
+def test_trace_program_on_a_sumitar_folder(models, tmp_path, name, dtype):
+    """The program on a folder with both kinds of layer, on one without a paged cache and on one without delta-rule layers."""
+    cfg, _ = ST.CONFIGS[name]
     requests = make_requests(cfg, [70, 9, 33, 50, 21], seed=6)
     steps = traces.mixed(requests, seed=1)
     need = traces.max_live_tokens(steps, round_to=64)
     out = tmp_path / "out"
-    folder = model_for(models, "B", dtype)
+    folder = model_for(models, name, dtype)
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
                            "--out", str(out), "--max-tokens", str(need)],
                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
