@@ -814,6 +814,52 @@ tanh_norm_fold_pair_kernel(float* __restrict__ h, const T* __restrict__ y1, cons
     }
 }
 
+// The same with eight entries per access and C such groups per thread (hidden <= 2048 C, a multiple of 8; every pointer on a
+// 32-byte boundary).  Everything a thread needs (its entries of both branches, of the stream and of the five vectors) is asked
+// for before the block's sums are taken, so the sums wait for memory once and the rest finds its operands on the chip.
+template <typename T, int C>
+__global__ void __launch_bounds__(256)
+tanh_norm_fold_pair_vec8_kernel(float* __restrict__ h, const T* __restrict__ y1, const T* __restrict__ y2, const float* __restrict__ w1,
+                                const float* __restrict__ w2, float eps, TanhNormArgs post, TanhNormArgs pre, T* __restrict__ out,
+                                const int* __restrict__ row_idx, int write_h, int hidden) {
+    __shared__ float scratch[96];
+    const size_t r = blockIdx.x, row = row_idx ? (size_t)row_idx[r] : r;
+    float a[C][8], b[C][8], hv[C][8], g1[C][8], g2[C][8], pw[C][8], pb[C][8];
+    float s1 = 0.0f, s2 = 0.0f, unused = 0.0f;
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int j = (c * 256 + threadIdx.x) * 8;
+        if (j < hidden) {
+            load8(y1 + row * hidden + j, a[c]); load8(y2 + row * hidden + j, b[c]); load8(h + row * hidden + j, hv[c]);
+            load8(w1 + j, g1[c]); load8(w2 + j, g2[c]); load8(post.w + j, pw[c]); load8(post.b + j, pb[c]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { s1 = fmaf(a[c][e], a[c][e], s1); s2 = fmaf(b[c][e], b[c][e], s2); }
+        }
+    }
+    block_sum3(s1, s2, unused, scratch);
+    const float r1 = 1.0f / sqrtf(s1 / (float)hidden + eps), r2 = 1.0f / sqrtf(s2 / (float)hidden + eps);
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        const int j = (c * 256 + threadIdx.x) * 8;
+        if (j < hidden) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float joined = 0.5f * ((a[c][e] * r1) * g1[c][e] + (b[c][e] * r2) * g2[c][e]);
+                v[e] = hv[c][e] + (tanhf(post.a * joined) * pw[c][e] + pb[c][e]);
+            }
+            if (write_h) store8(h + row * hidden + j, v);
+            if (out) {
+                float qw[8], qb[8], o[8];
+                load8(pre.w + j, qw); load8(pre.b + j, qb);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = tanhf(pre.a * v[e]) * qw[e] + qb[e];
+                store8(out + r * hidden + j, o);
+            }
+        }
+    }
+}
+
 ZI_EXPORT int zi_tanh_norm_fold_pair(float* h, const void* y1, const void* y2, int dtype, const float* w1, const float* w2, float eps, float post_a,
                                      const float* post_w, const float* post_b, float pre_a, const float* pre_w, const float* pre_b, void* out,
                                      const int* row_idx, int rows, int hidden, int write_h, cudaStream_t stream) {
@@ -823,9 +869,20 @@ ZI_EXPORT int zi_tanh_norm_fold_pair(float* h, const void* y1, const void* y2, i
     if (out && (!pre_w || !pre_b)) return zi_fail("tanh_norm_fold_pair: an output needs the norm that makes it");
     if (row_idx && write_h) return zi_fail("tanh_norm_fold_pair: chosen rows leave the stream as it is");
     const TanhNormArgs post{post_a, post_w, post_b}, pre{pre_a, pre_w, pre_b};
+    // which form runs depends on the sizes and on where the buffers start, never on the rows of the step
+    const bool vec = hidden % 8 == 0 && hidden <= 3 * 2048 &&
+                     (((size_t)h | (size_t)y1 | (size_t)y2 | (size_t)out | (size_t)w1 | (size_t)w2 | (size_t)post_w | (size_t)post_b |
+                       (size_t)pre_w | (size_t)pre_b) & 31) == 0;
     ZI_DISPATCH(dtype, T, {
-        tanh_norm_fold_pair_kernel<T><<<rows, hidden >= 2048 ? 256 : 128, (size_t)hidden * 2 * sizeof(float), stream>>>(
-            h, (const T*)y1, (const T*)y2, w1, w2, eps, post, pre, (T*)out, row_idx, write_h, hidden);
+        if (vec && hidden <= 2048)
+            tanh_norm_fold_pair_vec8_kernel<T, 1><<<rows, 256, 0, stream>>>(h, (const T*)y1, (const T*)y2, w1, w2, eps, post, pre, (T*)out, row_idx, write_h, hidden);
+        else if (vec && hidden <= 4096)
+            tanh_norm_fold_pair_vec8_kernel<T, 2><<<rows, 256, 0, stream>>>(h, (const T*)y1, (const T*)y2, w1, w2, eps, post, pre, (T*)out, row_idx, write_h, hidden);
+        else if (vec)
+            tanh_norm_fold_pair_vec8_kernel<T, 3><<<rows, 256, 0, stream>>>(h, (const T*)y1, (const T*)y2, w1, w2, eps, post, pre, (T*)out, row_idx, write_h, hidden);
+        else
+            tanh_norm_fold_pair_kernel<T><<<rows, hidden >= 2048 ? 256 : 128, (size_t)hidden * 2 * sizeof(float), stream>>>(
+                h, (const T*)y1, (const T*)y2, w1, w2, eps, post, pre, (T*)out, row_idx, write_h, hidden);
     });
     return zi_check_launch("tanh_norm_fold_pair");
 }
