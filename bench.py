@@ -384,7 +384,7 @@ def sumitar_config(width, heads, ff, window, layers, vocab, experts, top, expert
     as the three of Qwen2's beside it) and routed (`experts` of `expert_ff` plus two that return their input, `top` chosen, a
     gated shared expert) by turns."""
     kv = 2 if heads <= 12 else 4
-    left = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": window}, "rot": {"base": 1000000.0, "dims": dim // 2},
+    left = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": window}, "rot": {"base": 500000.0, "dims": dim // 2},
             "scale": dim ** -0.5}
     dense = {"kind": "dense", "ff": ff}
     moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "identity": 2, "top": top}, "shared": {"ff": shared_ff}}

@@ -55,7 +55,7 @@ SM_B = {
         _with(_parallel(_left(2, 1, 64, 64, 40, 64, 10000.0, 0.125), 2, 32, 64), _moe(6, 2, 2, 48, shared=64)),
         _with(_delta(2, 2, 32, 64, 4), _dense(160)),
         _with(_parallel(_left(4, 4, 128, 128, 70, 32, 300.0, 0.09), 2, 64, 32), None),
-        _with(_parallel(_left(4, 2, 64, 128, 33, 16, 1e6, 0.11), 4, 48, 64), _dense(64)),
+        _with(_parallel(_left(4, 2, 64, 128, 33, 24, 2e5, 0.11), 3, 40, 64), _dense(64)),
     ],
 }
 # sizes that fit no vector width: heads of 24 with values of 40 and 2 turned entries, a window of 3, one forget-gate head, a

@@ -50,6 +50,11 @@ def test_layers_and_their_parts():
     bare = spec.layers[2].ffn.params
     assert bare["shared"] is None and bare["shared_gate_name"] is None and bare["identity"] == 0
     assert spec.tie_word_embeddings
+    # without a mask the layer sees, and its cache keeps, every key
+    cfg = copy.deepcopy(ST.SM_A)
+    cfg["layers"][0]["mixer"]["left"]["mask"] = None
+    free = spec_of(cfg).layers[0].mixer.params
+    assert free["window"] is None and dict(Model(spec_of(cfg)).cache_needs())[0] == PagedKVNeed(2, 32, None, planes=2)
 
 
 def test_tensor_names():
@@ -88,7 +93,7 @@ def test_caches_and_states():
     (lambda c: c["layers"][0]["mixer"]["left"].update(heads=3), "kv_heads"),
     (lambda c: c["layers"][0]["mixer"]["left"]["rot"].update(dims=7), "rot"),
     (lambda c: c["layers"][0]["mixer"]["left"]["rot"].update(dims=64), "rot"),
-    (lambda c: c["layers"][0]["mixer"]["left"].pop("mask"), "mask"),
+    (lambda c: c["layers"][0]["mixer"]["left"].update(mask={"size": 0}), "mask"),
     (lambda c: c["layers"][0]["mixer"].pop("right"), "right"),
     (lambda c: c["layers"][1]["mixer"].update(kv_heads=3), "kv_heads"),
     (lambda c: c["layers"][1]["mixer"].pop("conv"), "conv"),

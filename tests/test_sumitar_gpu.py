@@ -85,7 +85,7 @@ def test_the_tanh_norm_on_both_sides_of_a_float32_stream(dtype, rows, hidden):
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("rows,hidden,eps", [(1, 40, 1e-5), (9, 192, 1e-6), (4, 73, 1e-4), (2, 2048, 1e-5)])
+@pytest.mark.parametrize("rows,hidden,eps", [(1, 40, 1e-5), (9, 176, 1e-6), (4, 73, 1e-4), (2, 2048, 1e-5)])
 def test_two_branches_joined_by_their_unit_rows(dtype, rows, hidden, eps):
     """(U(x) wx + U(z) wz) / 2; one input so small that the epsilon inside the root shows."""
     from zedinfer_b200 import ops
@@ -338,7 +338,7 @@ def test_delta_rule_with_a_decay_per_head_over_portions_and_slots_used_again(dty
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("heads,dim,vdim", [(3, 16, 24), (1, 40, 20), (4, 8, 136), (2, 136, 16), (5, 48, 64), (1, 256, 4)])
+@pytest.mark.parametrize("heads,dim,vdim", [(3, 16, 24), (1, 40, 20), (4, 8, 136), (2, 136, 16), (5, 40, 64), (1, 256, 4)])
 def test_forget_gate_mixer_over_portions_and_slots_used_again(dtype, heads, dim, vdim):
     from zedinfer_b200.cache import CacheManager
     from zedinfer_b200.parts import ForgetGateMixer
@@ -375,7 +375,7 @@ SCHEDULE_AB = [[("a", 9), ("b", 2)], [("b", 1), ("a", 1)], [("a", 1)], [("a", 33
 @pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("heads,kv,dim,vdim,window,rot_dims,base,page", [
     (4, 2, 32, 16, 13, 16, 5000.0, 4), (2, 1, 64, 64, 40, 64, 10000.0, 16), (4, 4, 128, 128, 21, 32, 300.0, 16), (3, 3, 24, 40, 3, 2, 77.0, 8),
-    (6, 3, 64, 128, 29, 16, 1e6, 16), (1, 1, 8, 8, 1, 8, 10.0, 8)])
+    (8, 2, 64, 128, 29, 24, 2e5, 16), (1, 1, 8, 8, 1, 8, 10.0, 8)])
 def test_windowed_attention_with_biases_and_a_number_per_head(dtype, heads, kv, dim, vdim, window, rot_dims, base, page):
     """Over portions and single tokens of two requests in shared steps; the heads' numbers differ widely, so one that is
     left out or given to the wrong head shows."""
@@ -401,7 +401,7 @@ def test_windowed_attention_with_biases_and_a_number_per_head(dtype, heads, kv, 
 
 @pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("dim,vdim,window,page,rot_dims,base", [(32, 24, 150, 16, 16, 50.0), (64, 128, 97, 8, 32, 300.0), (128, 128, 256, 16, 64, 1000.0),
-                                                              (16, 24, 580, 4, 16, 20.0), (64, 64, 96, 16, 16, 1e6)])
+                                                              (16, 24, 580, 4, 16, 20.0), (64, 64, 80, 16, 24, 2e5)])
 def test_one_key_answers_just_inside_the_window_and_none_just_outside(dtype, dim, vdim, window, page, rot_dims, base):
     """One head whose scores rest on the turned span alone, 600 tokens.  A query aligned with the key that is window - 1
     tokens back gets that key's value; one aligned with the key window tokens back does not (all its other scores are zero, it
@@ -453,7 +453,7 @@ def test_one_key_answers_just_inside_the_window_and_none_just_outside(dtype, dim
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("hidden,ff", [(64, 80), (52, 36), (192, 256), (48, 8)])
+@pytest.mark.parametrize("hidden,ff", [(64, 80), (52, 36), (160, 224), (48, 8)])
 def test_feed_forward_of_normed_powers(dtype, hidden, ff):
     from zedinfer_b200.parts import PolyNormMLP
     part = PolyNormMLP(hidden, ff, 1e-5)
@@ -475,7 +475,7 @@ def _bare_context(n, dtype):
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("experts,identity,top,ff,shared", [(12, 2, 2, 96, 128), (5, 1, 6, 24, 40), (3, 2, 1, 24, None), (1, 1, 2, 8, None), (4, 0, 3, 32, 16)])
+@pytest.mark.parametrize("experts,identity,top,ff,shared", [(10, 3, 2, 80, 112), (5, 1, 6, 24, 40), (3, 2, 1, 24, None), (1, 1, 2, 8, None), (4, 0, 3, 32, 16)])
 @pytest.mark.parametrize("tokens", [5, 150])
 def test_routed_feed_forward_with_experts_that_return_their_input(dtype, experts, identity, top, ff, shared, tokens):
     """Few tokens (the weight-streaming grouped product) and many (the tensor-core one in bfloat16).  In bfloat16 the part's

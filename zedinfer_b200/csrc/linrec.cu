@@ -7,8 +7,8 @@
 //                                    (or, with decay_per_head, one decay per head: a and dt_bias then hold one number per head)
 //                             decay  S <- lambda S + k v^T;  o = S^T q          (lambda a constant of the head)
 //                             forget S <- diag(f) S + (1 - f) v^T;  o = S^T q   with the gate per head and key entry
-//                                    f = l + (1 - l) sigmoid(a), l a lower bound per head and key entry; the gate that
-//                                    forgets also decides what is written, there is no key
+//                                    f = l + (1 - l) sigmoid(a), l a lower bound per head and key entry; 1 - f stands
+//                                    where the other rules have a key
 //                           the state read from and written back to the request's slot
 //   zi_group_rmsnorm_gate   out = unit_rms_per_group(y) * w * gate(z), the gate sigmoid, SiLU or none
 //

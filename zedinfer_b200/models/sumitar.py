@@ -9,8 +9,8 @@ layer:
 * ``parallel``: two mixers read the same input and are joined as ``(U(left) * w_l + U(right) * w_r) / 2``.  ``left`` is
   grouped-query attention with biases on q, k and v, value heads of their own size, the first ``rot.dims`` entries of every
   query and key head turned in the rotate-half pairing, ``scale`` from the config times one learned number per head
-  (``temp``), and a window of ``mask.size`` keys.  ``right`` is linear attention whose forget gate, bounded below per entry,
-  also decides what is written (``forget_gate``).
+  (``temp``), and a window of ``mask.size`` keys.  ``right`` is a matrix-state recurrence with one gate per key entry, bounded below,
+  that fades the state and whose complement stands where a key would (``forget_gate``).
 * ``delta``: a gated delta rule with one decay per head, short causal convolutions on q, k and v, and a SiLU gate on the
   normed read-out (``gated_delta``).
 
@@ -79,7 +79,8 @@ def _left(m: Mapping[str, Any], where: str) -> Dict[str, Any]:
     if sizes["heads"] % sizes["kv_heads"]:
         raise ConfigError(f"config.json: {where}heads={sizes['heads']} is no multiple of kv_heads={sizes['kv_heads']}")
     sizes["scale"] = _num(m, "scale", where)
-    sizes["window"] = _int(_obj(m, "mask", where), "size", where + "mask.")
+    # a layer without a mask (null, or no key at all) sees every key
+    sizes["window"] = _int(_obj(m, "mask", where), "size", where + "mask.") if m.get("mask") is not None else None
     rot = _obj(m, "rot", where)
     sizes["rot_base"], sizes["rot_dims"] = _num(rot, "base", where + "rot."), _int(rot, "dims", where + "rot.")
     if not sizes["rot_base"] > 0.0 or sizes["rot_dims"] % 2 or sizes["rot_dims"] > sizes["dim"]:

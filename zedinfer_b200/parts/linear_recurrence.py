@@ -12,7 +12,7 @@ entries (head a reads query/key head ``a // (H / G)``) and values of ``vdim`` en
 ``gated_delta`` is the same rule with one decay per head, ``g = exp(-exp(A_log_a) softplus(Wa h + dt_bias_a))``, the decay's and
 the gate's inputs projected in one step each, and a SiLU gate: ``out = Wo (unit_rms_per_head(o) * w_norm * silu(Wg h))``.
 
-``forget_gate`` (linear attention in which the gate that forgets also decides what is written; there is no key):
+``forget_gate`` (one gate per key entry fades the state, and its complement stands where the other rules have a key):
 
     q = silu(Wq h);   v = Wv h;   f = l + (1 - l) sigmoid(Wf h + bf)          l [H, dim] a lower bound, f per head and key entry
     per head:   S <- diag(f) S + (1 - f) v^T;   o = S^T q
