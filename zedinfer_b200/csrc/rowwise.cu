@@ -1020,25 +1020,40 @@ ZI_EXPORT int zi_poly_norm(const void* z, int dtype, long long ldz, void* out, i
 }
 
 // ---------------------------------------------------------------------------------------
-// One gate per row:  g[n] = sigmoid(x[n, :] . w)  in float32 (x, w of any of the two types).  One block per row, the lanes'
-// sums in a fixed order.
+// One gate per row:  g[n] = sigmoid(x[n, :] . w)  in float32 (x, w of any of the two types).  One warp per row, eight rows
+// per block; a lane's terms in rising k, the lanes' sums in a fixed order.  VEC: eight entries per access (K and ldx multiples
+// of 8, pointers on 16- and 32-byte boundaries); which form runs depends on sizes and addresses, never on the rows.
 // ---------------------------------------------------------------------------------------
-template <typename T, typename TW>
-__global__ void __launch_bounds__(128)
-row_gate_kernel(const T* __restrict__ x, long long ldx, const TW* __restrict__ w, float* __restrict__ g, int K) {
-    __shared__ float scratch[32];
-    const size_t n = blockIdx.x;
+#define RG_WARPS 8
+template <typename T, typename TW, bool VEC>
+__global__ void __launch_bounds__(RG_WARPS * 32)
+row_gate_kernel(const T* __restrict__ x, long long ldx, const TW* __restrict__ w, float* __restrict__ g, int rows, int K) {
+    const int lane = threadIdx.x & 31;
+    const size_t n = (size_t)blockIdx.x * RG_WARPS + (threadIdx.x >> 5);
+    if (n >= (size_t)rows) return;
     float acc = 0.0f;
-    for (int k = threadIdx.x; k < K; k += blockDim.x) acc = fmaf(to_f32<T>(x[n * ldx + k]), to_f32<TW>(w[k]), acc);
-    acc = block_sum(acc, scratch);
-    if (threadIdx.x == 0) g[n] = 1.0f / (1.0f + expf(-acc));
+    if (VEC) {
+        for (int k = lane * 8; k < K; k += 256) {
+            float a[8], b[8];
+            load8(x + n * ldx + k, a); load8(w + k, b);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc = fmaf(a[e], b[e], acc);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(to_f32<T>(x[n * ldx + k]), to_f32<TW>(w[k]), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) g[n] = 1.0f / (1.0f + expf(-acc));
 }
 
 ZI_EXPORT int zi_row_gate(const void* x, int dtype, long long ldx, const void* w, int w_dtype, float* g, int rows, int K, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (K <= 0) return zi_fail("row_gate: K=%d", K);
+    const bool vec = K % 8 == 0 && ldx % 8 == 0 && (((size_t)x | (size_t)w) & 31) == 0;
+    const int blocks = (rows + RG_WARPS - 1) / RG_WARPS;
     ZI_DISPATCH(dtype, T, ZI_DISPATCH(w_dtype, TW, {
-        row_gate_kernel<T, TW><<<rows, 128, 0, stream>>>((const T*)x, ldx, (const TW*)w, g, K);
+        if (vec) row_gate_kernel<T, TW, true><<<blocks, RG_WARPS * 32, 0, stream>>>((const T*)x, ldx, (const TW*)w, g, rows, K);
+        else row_gate_kernel<T, TW, false><<<blocks, RG_WARPS * 32, 0, stream>>>((const T*)x, ldx, (const TW*)w, g, rows, K);
     }););
     return zi_check_launch("row_gate");
 }
